@@ -143,6 +143,14 @@ typedef struct tesserae_kernel_spec {
     int has_bias;    /* add bf16 bias[n] in the epilogue */
     int scale_mode;  /* TESSERAE_SCALE_* */
     int scatter;     /* 1: row-scattered output for tesserae_gemm_ksplit_scatter (unscaled kernels, no bias) */
+    /* Optional overrides of the kernel's tuning choices, "NAME=VALUE;NAME=VALUE" (NULL or "" = the defaults).
+     * The kernel a plan runs is a function of its spec alone; nothing is read from the environment.  Names:
+     *   GROUP_M=1..64          M-tiles per raster group of the persistent tile order
+     *   STORE_BUFS=2..4        dense kernel: staging buffers per epilogue warp
+     *   FP8_PROMO_WARPS=8|16   block-scaled FP8: promotion warps
+     *   FP8_SPLIT=0|1          block-scaled FP8: one MMA chain per tile width / per 128 columns
+     * An unknown name or a value out of range fails with IncompatibleTile. */
+    const char* tuning;
 } tesserae_kernel_spec;
 
 /* Kernel_desc.t (lib/kernel/kernel_desc.ml:12-26), flattened to integers. */
@@ -331,6 +339,14 @@ int tesserae_nccl_load(const char* path_or_null);
 int tesserae_nccl_version(int* version);
 int tesserae_nccl_unique_id(void* id128);
 int tesserae_nccl_comm_init(void** comm, int world, int rank, const void* id128);
+/* comm_init that gives up: the communicator is created non-blocking and polled; if it is not ready after
+ * `timeout_ms` (a rank never joined, a peer died during set-up) it is aborted, *comm is NULL and the call fails
+ * with a message that names the timeout.  Needs NCCL 2.14 or later.  Collectives on such a communicator are
+ * settled inside the wrappers below, so callers see the same 0 / non-zero contract. */
+int tesserae_nccl_comm_init_deadline(void** comm, int world, int rank, const void* id128, int timeout_ms);
+/* ncclCommAbort: tears a communicator down without waiting for its peers or for work in flight; the call for
+ * the path where a rank has failed and ncclCommDestroy would block.  NULL is a no-op. */
+int tesserae_nccl_comm_abort(void* comm);
 int tesserae_nccl_comm_destroy(void* comm);
 int tesserae_nccl_reduce_scatter_f32(void* comm, const void* send, void* recv, size_t recv_count, void* stream);
 int tesserae_nccl_all_reduce_f32(void* comm, const void* send, void* recv, size_t count, void* stream);
@@ -365,17 +381,23 @@ int tesserae_gemm_ksplit_scatter(tesserae_gemm_plan* plan, const void* a, const 
  * the reference.  It is for hosts that cannot call cudaMalloc at the moment they need the GEMM: a process
  * whose own allocator already owns nearly all GPU memory (a raw cudaMalloc would fail there), or a serving
  * loop that cannot take the device-wide synchronisation an allocation or free implies.  The fp32 partials
- * go to a fixed array inside the library image; every GPU that loads the library holds that array
- * (TESSERAE_NOALLOC_MAX_ELEMS floats = 32 MiB) until the process exits.
+ * go to a fixed array inside the library image (TESSERAE_NOALLOC_MAX_ELEMS floats = 32 MiB per GPU).
  *   - Limit: m * n * k_splits <= TESSERAE_NOALLOC_MAX_ELEMS, otherwise the call fails with a message naming
  *     both numbers; nothing is launched.
- *   - The first call on each device looks up the array's device address (with that device current); make
- *     that first call before starting any stream capture.
+ *   - The first call on each device is the set-up call: it looks up the array's device address (with that
+ *     device current), and because CUDA loads device code lazily that lookup is also the moment the driver
+ *     reserves the 32 MiB on that device (they are then held until the process exits).  Make that first call
+ *     at start-up, before the host's own allocator takes the remaining memory and before any stream capture;
+ *     a call that is refused for its size still performs the set-up, so a start-up call needs no real work.
+ *     From the second call on a device nothing is allocated or reserved: free device memory is the same
+ *     before and after a call.
+ *   - The looked-up address is cached per device ordinal.  If the host resets a device's primary context
+ *     (cudaDeviceReset) the cached address is stale; the library is not meant to outlive such a reset.
  *   - All calls share the one array, which keeps the previous call's partials.  Nothing needs clearing (the
  *     GEMM overwrites every element it later sums), but two calls that overlap on the GPU (different
  *     streams, no ordering between them) race on it.
  *   - Neither this call nor anything under it calls cudaMalloc, cudaFree or an allocating library routine;
- *     the plan is created beforehand. */
+ *     the plan is created beforehand, and must be used with the device it was created on current. */
 #define TESSERAE_NOALLOC_MAX_ELEMS 8388608
 size_t tesserae_gemm_ksplit_noalloc_max_elems(void);
 int tesserae_gemm_ksplit_run_noalloc(tesserae_gemm_plan* plan, const void* a, const void* b, void* c_bf16,
@@ -389,9 +411,6 @@ int tesserae_gemm_status(tesserae_gemm_plan* plan, uint32_t* status);
  * completed) and *waited_cycles_out the cycles the wait took.  The kernel returns normally and the
  * context stays usable.  No counterpart in the reference, whose waits are unbounded. */
 int tesserae_wait_selftest(int64_t budget_cycles, uint32_t* status_out, int64_t* waited_cycles_out);
-/* Debugging aid: copies the plan's 16 KB device status block to `dst` (word 0 = the status word;
- * kernels compiled with TESSERAE_TRACE=1 in the environment also leave clock samples there). */
-int tesserae_gemm_debug_read(tesserae_gemm_plan* plan, void* dst, size_t n_bytes);
 /* Same call with host buffers in the operand's own element type: copies A, B (and bias) to
  * the device, runs, copies C back, all inside the call.  Synchronous. */
 int tesserae_gemm_run_host(tesserae_gemm_plan* plan, const void* a, const void* b, void* c, const void* bias,

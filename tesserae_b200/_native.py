@@ -16,7 +16,7 @@ class KernelSpecC(C.Structure):
     _fields_ = [("name", C.c_char_p), ("arch", C.c_int), ("elem", C.c_int),
                 ("tile_m", C.c_int), ("tile_n", C.c_int), ("tile_k", C.c_int), ("stages", C.c_int),
                 ("cta_group", C.c_int), ("out_elem", C.c_int), ("has_bias", C.c_int), ("scale_mode", C.c_int),
-                ("scatter", C.c_int)]
+                ("scatter", C.c_int), ("tuning", C.c_char_p)]
 
 
 class KernelDescC(C.Structure):
@@ -152,6 +152,8 @@ SIGNATURES = {
     "tesserae_nccl_version": (C.c_int, [C.POINTER(C.c_int)]),
     "tesserae_nccl_unique_id": (C.c_int, [C.c_void_p]),
     "tesserae_nccl_comm_init": (C.c_int, [C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_void_p]),
+    "tesserae_nccl_comm_init_deadline": (C.c_int, [C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_void_p, C.c_int]),
+    "tesserae_nccl_comm_abort": (C.c_int, [C.c_void_p]),
     "tesserae_nccl_comm_destroy": (C.c_int, [C.c_void_p]),
     "tesserae_nccl_reduce_scatter_f32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "tesserae_nccl_all_reduce_f32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
@@ -168,7 +170,6 @@ SIGNATURES = {
     "tesserae_gemm_ksplit_noalloc_max_elems": (C.c_size_t, []),
     "tesserae_gemm_ksplit_run_noalloc": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_int64,
                                                    C.c_int64, C.c_int64, C.c_int, C.c_void_p]),
-    "tesserae_gemm_debug_read": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t]),
     "tesserae_gemm_status": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint32)]),
     "tesserae_gemm_run_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_float,
                                          C.c_int64, C.c_int64, C.c_int64]),

@@ -34,13 +34,16 @@ class KernelSpec:
     has_bias: int = 0
     scale_mode: int = 0
     scatter: int = 0
+    tuning: str = ""
     _keep: list = field(default_factory=list, repr=False, compare=False)
 
     def to_c(self) -> N.KernelSpecC:
         name = self.name.encode()
         self._keep.append(name)
+        tuning = self.tuning.encode() if self.tuning else None
+        self._keep.append(tuning)
         return N.KernelSpecC(name, self.arch, self.elem, self.tile[0], self.tile[1], self.tile[2], self.stages,
-                             self.cta_group, self.out_elem, self.has_bias, self.scale_mode, self.scatter)
+                             self.cta_group, self.out_elem, self.has_bias, self.scale_mode, self.scatter, tuning)
 
 
 class LowerError(Exception):

@@ -20,8 +20,8 @@ constexpr int kSmemLimit = 232448;   // 227 KB of dynamic shared memory per CTA 
 
 // Dynamic shared memory of each kernel family; mirrors kSmemTotal in the .cuh plus the
 // 1024-byte alignment slack.
-int dense_smem_bytes(int cta_group, int block_n, int stages, int store_bufs) {
-    const int stage = 128 * 128 + (block_n / cta_group) * 128;
+int dense_smem_bytes(int cta_group, int block_n, int stages, int store_bufs, int row_bytes) {
+    const int stage = (128 + block_n / cta_group) * row_bytes;
     return stages * stage + 4 * store_bufs * 4096 + (2 * stages + 4) * 8 + 16 + 1024;
 }
 int fp8_smem_bytes(int cta_group, int block_n, int stages, int promo_warps, int out_bytes) {
@@ -44,7 +44,7 @@ int smem_bytes_for(const KernelConfig& c, int stages) {
     const int ob = c.out_elem == TESSERAE_F32 ? 4 : 2;
     if (c.scale_mode == TESSERAE_SCALE_FP8_BLOCK) return fp8_smem_bytes(c.cta_group, c.block_n, stages, c.promo_warps, ob);
     if (c.scale_mode == TESSERAE_SCALE_NVFP4) return nvfp4_smem_bytes(c.cta_group, c.block_n, stages);
-    return dense_smem_bytes(c.cta_group, c.block_n, stages, c.store_bufs);
+    return dense_smem_bytes(c.cta_group, c.block_n, stages, c.store_bufs, 16 << c.desc.swizzle.b);
 }
 
 std::string sanitize(const char* name) {
@@ -52,6 +52,29 @@ std::string sanitize(const char* name) {
     for (char& c : s) if (!isalnum((unsigned char)c) && c != '_') c = '_';
     if (isdigit((unsigned char)s[0])) s = "k_" + s;
     return s;
+}
+
+// "NAME=VALUE;NAME=VALUE" -> pairs; false on a malformed entry.
+bool parse_tuning(const char* text, std::vector<std::pair<std::string, int>>* out, std::string* bad) {
+    if (!text) return true;
+    std::string s(text);
+    size_t at = 0;
+    while (at < s.size()) {
+        size_t end = s.find(';', at);
+        if (end == std::string::npos) end = s.size();
+        std::string item = s.substr(at, end - at);
+        at = end + 1;
+        while (!item.empty() && isspace((unsigned char)item.back())) item.pop_back();
+        while (!item.empty() && isspace((unsigned char)item.front())) item.erase(item.begin());
+        if (item.empty()) continue;
+        const size_t eq = item.find('=');
+        if (eq == std::string::npos || eq == 0 || eq + 1 >= item.size()) { *bad = item; return false; }
+        char* tail = nullptr;
+        const long v = strtol(item.c_str() + eq + 1, &tail, 10);
+        if (*tail != '\0') { *bad = item; return false; }
+        out->emplace_back(item.substr(0, eq), int(v));
+    }
+    return true;
 }
 
 std::string strip_pragma_once(const char* text) {
@@ -99,20 +122,52 @@ int derive_config(const tesserae_kernel_spec& ks, KernelConfig* cfg, std::string
         if (msg) *msg = "IncompatibleTile: scattered output is for unscaled kernels with fp32 output and no bias";
         return spec::IncompatibleTile;
     }
-    // Staging depth of the dense epilogue: deeper when the stores may cross NVLink.  TESSERAE_STORE_BUFS (2|3|4) overrides.
+    // Staging depth of the dense epilogue: deeper when the stores may cross NVLink.
     c.store_bufs = c.scatter ? 4 : 2;
-    if (const char* e = getenv("TESSERAE_STORE_BUFS")) { const int v = atoi(e); if (v >= 2 && v <= 4) c.store_bufs = v; }
+    // The spec's own tuning overrides (nothing is read from the environment).
+    int want_promo_warps = 0;
+    {
+        std::vector<std::pair<std::string, int>> tv;
+        std::string bad;
+        if (!parse_tuning(ks.tuning, &tv, &bad)) {
+            if (msg) *msg = "IncompatibleTile: malformed tuning entry '" + bad + "' (want NAME=VALUE)";
+            return spec::IncompatibleTile;
+        }
+        for (const auto& kv : tv) {
+            const std::string& key = kv.first;
+            const int v = kv.second;
+            bool ok = true;
+            if (key == "GROUP_M") { ok = v >= 1 && v <= 64; c.group_m = v; }
+            else if (key == "STORE_BUFS") { ok = v >= 2 && v <= 4; c.store_bufs = v; }
+            else if (key == "FP8_PROMO_WARPS") { ok = v == 8 || v == 16; want_promo_warps = v; }
+            else if (key == "FP8_SPLIT") { ok = v == 0 || v == 1; c.fp8_split = v; }
+            else { if (msg) *msg = "IncompatibleTile: unknown tuning name '" + key + "'"; return spec::IncompatibleTile; }
+            if (!ok) {
+                if (msg) *msg = "IncompatibleTile: tuning value out of range: " + key + "=" + std::to_string(v);
+                return spec::IncompatibleTile;
+            }
+        }
+    }
     c.block_m = 128;
     c.block_n = ks.tile_n;
     c.block_k = ks.tile_k;
     c.threads = spec::thread_count(desc.cluster);
 
-    // What the hand-written mainloops cover: 128 rows per CTA, one 128-byte swizzle row of K per
-    // stage (Swizzle<3,4,3>), N a multiple of the store chunk and of 16 per CTA.
+    // What the hand-written mainloops cover: 128 rows per CTA, one swizzle row of K per stage, N a multiple
+    // of the store chunk and of 16 per CTA.  The swizzle is the one Swizzle.smem_selector derives from the tile
+    // (lib/core/swizzle.ml:46-56): the row a stage holds must be exactly the 16 << B bytes that Swizzle<B,4,3>
+    // permutes, B in 1..3 for the dense kernels; the block-scaled kernels need the 128-byte row (their scale
+    // blocks are one row wide).
     if (ks.tile_m != 128) { if (msg) *msg = "IncompatibleTile: tile.m must be 128 (rows per CTA)"; return spec::IncompatibleTile; }
-    if (int64_t(ks.tile_k) * spec::elem_bits(ks.elem) / 8 != 128 || desc.swizzle.b != 3) {
-        if (msg) *msg = "IncompatibleTile: tile.k must span exactly 128 bytes (Swizzle<3,4,3>)";
-        return spec::IncompatibleTile;
+    {
+        const int64_t row_bytes = int64_t(ks.tile_k) * spec::elem_bits(ks.elem) / 8;
+        const bool scaled = ks.scale_mode != TESSERAE_SCALE_NONE;
+        if (desc.swizzle.b < 1 || desc.swizzle.b > 3 || row_bytes != (int64_t(16) << desc.swizzle.b) ||
+            (scaled && desc.swizzle.b != 3)) {
+            if (msg) *msg = scaled ? "IncompatibleTile: tile.k must span exactly 128 bytes (Swizzle<3,4,3>) for a block-scaled kernel"
+                                   : "IncompatibleTile: tile.k must span 32, 64 or 128 bytes (Swizzle<1..3,4,3>)";
+            return spec::IncompatibleTile;
+        }
     }
     const int chunk = (c.out_elem == TESSERAE_F32) ? 32 : 64;
     if (c.block_n < 16 * c.cta_group || c.block_n > 256 || c.block_n % (16 * c.cta_group) != 0 || c.block_n % chunk != 0) {
@@ -132,14 +187,16 @@ int derive_config(const tesserae_kernel_spec& ks, KernelConfig* cfg, std::string
     if (c.scale_mode == TESSERAE_SCALE_FP8_BLOCK) {
         // Promotion warps on top of the producer and MMA warps.  8 (two per scheduler) measured
         // faster than 16 on the 256-wide tile: the TMEM reads contend with the running MMA, not with
-        // each other.  TESSERAE_FP8_PROMO_WARPS overrides the choice (8 or 16) for experiments.
+        // each other.
         c.promo_warps = 8;
-        if (const char* e = getenv("TESSERAE_FP8_PROMO_WARPS")) {
-            const int v = atoi(e);
-            if ((v == 8 || v == 16) && (c.block_n / (v / 4)) % ((c.out_elem == TESSERAE_F32) ? 32 : 64) == 0) c.promo_warps = v;
+        if (want_promo_warps) {
+            if ((c.block_n / (want_promo_warps / 4)) % ((c.out_elem == TESSERAE_F32) ? 32 : 64) != 0) {
+                if (msg) *msg = "IncompatibleTile: FP8_PROMO_WARPS=" + std::to_string(want_promo_warps) + " leaves a warp less than one store chunk of columns";
+                return spec::IncompatibleTile;
+            }
+            c.promo_warps = want_promo_warps;
         }
         c.threads = 128 + 32 * c.promo_warps;     // warpgroup 0 (producer, MMA issuer, two idle warps) + promotion warps
-        if (const char* e = getenv("TESSERAE_FP8_SPLIT")) c.fp8_split = (*e != '0');
         if (c.cta_group == 2 && c.fp8_split) c.b_box_rows = 64;  // 64 rows per CTA and 128-column MMA group
         if (c.block_n != 128 && c.block_n != 256) {
             if (msg) *msg = "IncompatibleTile: FP8 block scaling needs tile.n of 128 or 256 (whole 128x128 scale blocks)";
@@ -188,19 +245,19 @@ BackendOutput emit(const KernelConfig& c) {
              "#define TS_AB_FMT %s\n"
              "#define TS_OUT_F32 %d\n"
              "#define TS_HAS_BIAS %d\n"
-             "#define TS_PROMO_WARPS %d\n",
+             "#define TS_PROMO_WARPS %d\n"
+             "#define TS_SWIZZLE_B %d\n",
              o.filename.c_str(), c.block_m, c.block_n, c.block_k, spec::elem_name(c.elem), c.desc.swizzle.b,
              c.desc.swizzle.m, c.desc.swizzle.s, c.cta_group, c.stages, (long long)c.desc.pipeline.tile_bytes,
              c.cta_group, c.threads, c.smem_bytes, c.desc.sm_count, c.name.c_str(), c.cta_group, c.block_n, c.stages,
              (fp8 || s8) ? 1 : 2, fp8 ? "TS_KIND_F8F6F4" : s8 ? "TS_KIND_I8" : "TS_KIND_F16",
              fp8 ? "TS_FMT_E4M3" : s8 ? "TS_FMT_S8" : (c.elem == TESSERAE_F16 ? "TS_FMT_F16" : "TS_FMT_BF16"),
-             c.out_elem == TESSERAE_F32 ? 1 : 0, c.has_bias, c.promo_warps ? c.promo_warps : 8);
+             c.out_elem == TESSERAE_F32 ? 1 : 0, c.has_bias, c.promo_warps ? c.promo_warps : 8, c.desc.swizzle.b);
     o.includes = buf;
     if (c.scatter) o.includes += "#define TS_SCATTER 1\n";
     if (c.scale_mode == TESSERAE_SCALE_NONE) o.includes += "#define TS_STORE_BUFS " + std::to_string(c.store_bufs) + "\n";
-    if (const char* e = getenv("TESSERAE_TRACE")) if (*e == '1') o.includes += "#define TS_TRACE 1\n";
     if (c.scale_mode == TESSERAE_SCALE_FP8_BLOCK) o.includes += std::string("#define TS_FP8_SPLIT ") + (c.fp8_split ? "1\n" : "0\n");
-    if (const char* e = getenv("TESSERAE_GROUP_M")) if (atoi(e) > 0) o.includes += "#define TS_GROUP_M " + std::to_string(atoi(e)) + "\n";
+    o.includes += "#define TS_GROUP_M " + std::to_string(c.group_m) + "\n";
     o.helpers = strip_pragma_once(kSrcPtxSm100);
     const bool block_fp8 = c.scale_mode == TESSERAE_SCALE_FP8_BLOCK;
     const bool nvfp4 = c.scale_mode == TESSERAE_SCALE_NVFP4;

@@ -23,6 +23,7 @@ struct KernelConfig {
     int scatter = 0;         // row-scattered output (dense kernel only)
     int promo_warps = 0;     // promotion warps of the FP8 block-scaled kernel (0 elsewhere)
     int store_bufs = 2;      // dense kernel: staging buffers per epilogue warp (4 when the stores cross NVLink)
+    int group_m = 8;         // M-tiles per raster group of the persistent tile order
     int fp8_split = 1;       // FP8 block-scaled: one MMA chain and TMEM buffer per 128 columns (else per tile width)
     int b_box_rows = 128;    // rows of B one TMA load brings (the FP8 block-scaled pair kernel loads B per 128-column MMA group)
     int threads = 192;

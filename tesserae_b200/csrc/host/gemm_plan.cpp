@@ -50,9 +50,8 @@ struct tesserae_gemm_plan {
 
 namespace {
 
-// Device status block of a plan: word 0 is the error word the kernels OR their timeout bits into;
-// the rest is scratch that kernels built with TS_TRACE fill with clock64 samples.
-constexpr size_t kStatusBytes = 16384;
+// Device status block of a plan: word 0 is the error word the kernels OR their timeout bits into.
+constexpr size_t kStatusBytes = 256;
 
 double now_ms() {
     using namespace std::chrono;
@@ -66,6 +65,9 @@ char* dup_string(const std::string& s) {
 }
 
 int out_bytes(int out_elem) { return out_elem == TESSERAE_F32 ? 4 : 2; }
+
+// The epilogues stage C in 32-row x 128-byte buffers written under Swizzle<3,4,3>, whatever the operand tiles use.
+constexpr int kStoreSwizzleB = 3;
 
 // fp32 -> bf16 / f16 bits, round to nearest even (host side of Runtime.run).
 uint16_t f32_to_bf16(float f) {
@@ -345,11 +347,23 @@ int tesserae_gemm_plan_info(const tesserae_gemm_plan* p, int* cta_group, int* bl
     return 0;
 }
 
+// A plan's module, status word and staging live on the device that was current when it was created; a launch
+// with another device current would end in an opaque driver error (or tensor maps over the wrong memory).
+static int check_plan_device(const tesserae_gemm_plan* p, const char* what) {
+    int cur = -1;
+    if (cudaGetDevice(&cur) != cudaSuccess) return fail(std::string(what) + ": cannot read the current device");
+    if (cur != p->device)
+        return fail(std::string(what) + ": the plan was created on device " + std::to_string(p->device) +
+                    " but device " + std::to_string(cur) + " is current");
+    return 0;
+}
+
 // lda / ldb / ldc: row pitch in elements of A (M x K), B (N x K) and C (M x N); 0 = dense.
 static int gemm_launch(tesserae_gemm_plan* p, const void* a, int64_t lda, const void* b, int64_t ldb, void* c, int64_t ldc,
                        const tesserae_gemm_scales* scales, const void* bias,
                        float alpha, int64_t m, int64_t n, int64_t k, void* stream) {
     if (!p || !a || !b || !c) return fail("gemm_run: null argument");
+    if (int drc = check_plan_device(p, "gemm_run")) return drc;
     if (m <= 0 || n <= 0 || k <= 0) return fail("gemm_run: M, N and K must be positive");
     if (m > INT32_MAX || n > INT32_MAX || k > INT32_MAX) return fail("gemm_run: dimension exceeds 2^31-1");
     const KernelConfig& cfg = p->cfg;
@@ -380,11 +394,14 @@ static int gemm_launch(tesserae_gemm_plan* p, const void* a, int64_t lda, const 
     // For the 4-bit element the map addresses bytes: two values per byte along K.
     const uint64_t inner_ab = (cfg.elem == TESSERAE_F4E2M1) ? uint64_t(k) / 2 : uint64_t(k);
     const uint32_t box_k = (cfg.elem == TESSERAE_F4E2M1) ? 128u : uint32_t(cfg.block_k);
-    int rc = tesserae_tensor_map_2d(tm_a, cfg.elem, a, inner_ab, uint64_t(m), row_bytes_a, box_k, 128, 3);
+    // Operand tiles land in shared memory under the swizzle the descriptor was lowered with (Swizzle.smem_selector
+    // of the spec's tile); the output staging rows are always 128 bytes wide, hence Swizzle<3,4,3> for C.
+    const int op_swizzle = cfg.desc.swizzle.b;
+    int rc = tesserae_tensor_map_2d(tm_a, cfg.elem, a, inner_ab, uint64_t(m), row_bytes_a, box_k, 128, op_swizzle);
     if (rc == 0) rc = tesserae_tensor_map_2d(tm_b, cfg.elem, b, inner_ab, uint64_t(n), row_bytes_b, box_k,
-                                             uint32_t(cfg.b_box_rows), 3);
+                                             uint32_t(cfg.b_box_rows), op_swizzle);
     if (rc == 0) rc = tesserae_tensor_map_2d(tm_c, cfg.out_elem, c, uint64_t(n), uint64_t(m), uint64_t(ldc) * ob,
-                                             uint32_t(128 / ob), 32, 3);
+                                             uint32_t(128 / ob), 32, kStoreSwizzleB);
     if (rc != 0) return rc;
 
     const int64_t tile_m = 128 * cfg.cta_group;
@@ -466,6 +483,7 @@ int tesserae_gemm_ksplit_partials(tesserae_gemm_plan* p, const void* a, const vo
 int tesserae_gemm_ksplit_scatter(tesserae_gemm_plan* p, const void* a, const void* b, void* const* dst, int n_dst,
                                  int64_t rows_per_owner, int64_t m, int64_t n, int64_t k, void* stream) {
     if (!p || !a || !b || !dst) return fail("ksplit_scatter: null argument");
+    if (int drc = check_plan_device(p, "ksplit_scatter")) return drc;
     const KernelConfig& cfg = p->cfg;
     if (!cfg.scatter) return fail("ksplit_scatter: the plan's spec must have scatter = 1");
     if (n_dst < 1 || n_dst > 8) return fail("ksplit_scatter: n_dst must be in 1..8");
@@ -478,14 +496,15 @@ int tesserae_gemm_ksplit_scatter(tesserae_gemm_plan* p, const void* a, const voi
     struct alignas(64) { unsigned char m[8][128]; } tm_c;
     memset(&tm_c, 0, sizeof tm_c);
     const uint64_t row_bytes = uint64_t(k) * ebits / 8;
-    int rc = tesserae_tensor_map_2d(tm_a, cfg.elem, a, uint64_t(k), uint64_t(m), row_bytes, uint32_t(cfg.block_k), 128, 3);
+    const int op_swizzle = cfg.desc.swizzle.b;
+    int rc = tesserae_tensor_map_2d(tm_a, cfg.elem, a, uint64_t(k), uint64_t(m), row_bytes, uint32_t(cfg.block_k), 128, op_swizzle);
     if (rc == 0) rc = tesserae_tensor_map_2d(tm_b, cfg.elem, b, uint64_t(k), uint64_t(n), row_bytes, uint32_t(cfg.block_k),
-                                             uint32_t(cfg.block_n / cfg.cta_group), 3);
+                                             uint32_t(cfg.block_n / cfg.cta_group), op_swizzle);
     for (int g = 0; g < n_dst && rc == 0; ++g) {
         const int64_t rows = (m - g * rows_per_owner) < rows_per_owner ? (m - g * rows_per_owner) : rows_per_owner;
         if (rows <= 0) break;
         if (!dst[g]) return fail("ksplit_scatter: null destination");
-        rc = tesserae_tensor_map_2d(tm_c.m[g], TESSERAE_F32, dst[g], uint64_t(n), uint64_t(rows), uint64_t(n) * 4, 32, 32, 3);
+        rc = tesserae_tensor_map_2d(tm_c.m[g], TESSERAE_F32, dst[g], uint64_t(n), uint64_t(rows), uint64_t(n) * 4, 32, 32, kStoreSwizzleB);
     }
     if (rc != 0) return rc;
     const int64_t tile_m = 128 * cfg.cta_group;
@@ -509,15 +528,6 @@ int tesserae_gemm_ksplit_run(tesserae_gemm_plan* p, const void* a, const void* b
     int rc = tesserae_gemm_ksplit_partials(p, a, b, scratch, scratch_bytes, m, n, k, k_splits, stream);
     if (rc != 0) return rc;
     return tesserae_reduce_cast_bf16(scratch, k_splits, size_t(m) * size_t(n), alpha, c_bf16, size_t(m) * size_t(n), stream);
-}
-
-int tesserae_gemm_debug_read(tesserae_gemm_plan* p, void* dst, size_t n_bytes) {
-    if (!p || !dst) return fail("gemm_debug_read: null argument");
-    if (n_bytes > kStatusBytes) n_bytes = kStatusBytes;
-    cudaError_t rc = cudaDeviceSynchronize();
-    if (rc == cudaSuccess) rc = cudaMemcpy(dst, p->d_status, n_bytes, cudaMemcpyDeviceToHost);
-    if (rc != cudaSuccess) return fail(cudaGetErrorString(rc));
-    return 0;
 }
 
 int tesserae_gemm_status(tesserae_gemm_plan* p, uint32_t* status) {

@@ -8,8 +8,14 @@
 // caller passes in; this variant keeps that scratch in a fixed array inside the library image
 // instead, so the call allocates nothing.
 //
-// The array lives in every GPU context that loads the library, from load until process exit
-// (32 MiB per GPU), and bounds the problem: m * n * k_splits <= TESSERAE_NOALLOC_MAX_ELEMS.
+// The array bounds the problem: m * n * k_splits <= TESSERAE_NOALLOC_MAX_ELEMS (32 MiB of fp32).
+//
+// When the memory is reserved: CUDA loads a library's device code lazily, so the 32 MiB are taken
+// on a device when this file's module is first touched there, which is the address lookup of the
+// first call on that device, and are held until the process exits.  A host whose allocator is
+// about to take the rest of the GPU's memory must therefore make one call (any call: even one
+// that is refused for its size resolves the array first) per device at start-up, before its
+// allocator grows and before any stream capture.  From then on calls allocate nothing.
 #include "../../../include/tesserae_b200.h"
 #include "../rt/errors.hpp"
 
@@ -60,15 +66,17 @@ extern "C" size_t tesserae_gemm_ksplit_noalloc_max_elems(void) { return kMaxElem
 
 extern "C" int tesserae_gemm_ksplit_run_noalloc(tesserae_gemm_plan* plan, const void* a, const void* b, void* c_bf16,
                                                 float alpha, int64_t m, int64_t n, int64_t k, int k_splits, void* stream) {
+    // Resolve the array first: the first call on a device is what makes the driver load this module and reserve
+    // the array there, and a start-up call made for that purpose may well carry sizes that are refused below.
+    float* scratch = nullptr;
+    int rc = scratch_for_current_device(&scratch);
+    if (rc != 0) return rc;
     if (m <= 0 || n <= 0 || k <= 0 || k_splits < 1) return fail("ksplit_noalloc: M, N, K and k_splits must be positive");
     const unsigned __int128 need = (unsigned __int128)m * (unsigned __int128)n * (unsigned __int128)k_splits;
     if (need > kMaxElems)
         return fail("ksplit_noalloc: m * n * k_splits = " + std::to_string((unsigned long long)need) +
                     " fp32 partials exceed the built-in scratch of " + std::to_string(kMaxElems) +
                     " elements; use tesserae_gemm_ksplit_run with caller-provided scratch");
-    float* scratch = nullptr;
-    int rc = scratch_for_current_device(&scratch);
-    if (rc != 0) return rc;
     // The GEMM overwrites every partial element it later sums, so nothing has to be cleared first.
     return tesserae_gemm_ksplit_run(plan, a, b, c_bf16, scratch, kMaxElems * sizeof(float), alpha, m, n, k, k_splits, stream);
 }

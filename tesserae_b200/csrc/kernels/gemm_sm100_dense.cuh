@@ -24,6 +24,8 @@
 //   TS_BLOCK_N       tile width = MMA N (multiple of 16*TS_CTA_GROUP, <= 256)
 //   TS_STAGES        depth of the smem ring
 //   TS_ELEM_BYTES    2 (bf16/f16) or 1 (e4m3)
+//   TS_SWIZZLE_B     B of the operand tiles' Swizzle<B,4,3> (1..3), as Swizzle.smem_selector derives it from the
+//                    spec's tile.k: one stage holds 16 << B bytes of K per row
 //   TS_MMA_KIND      TS_KIND_F16, TS_KIND_F8F6F4 or TS_KIND_I8 (signed 8-bit operands, 32-bit integer accumulation)
 //   TS_AB_FMT        operand format code of the instruction descriptor
 //   TS_OUT_F32       0: bf16 output, 1: fp32 output
@@ -47,6 +49,9 @@ struct TsTensorMapArray8 { TsTensorMap m[8]; };
 #ifndef TS_GROUP_M
 #define TS_GROUP_M 8
 #endif
+#ifndef TS_SWIZZLE_B
+#define TS_SWIZZLE_B 3
+#endif
 
 namespace ts_dense {
 
@@ -54,10 +59,10 @@ constexpr ts_u32 kBlockM      = 128;                          // rows per CTA
 constexpr ts_u32 kTileM       = kBlockM * TS_CTA_GROUP;       // rows per MMA tile
 constexpr ts_u32 kBlockN      = TS_BLOCK_N;
 constexpr ts_u32 kLoadN       = kBlockN / TS_CTA_GROUP;       // B rows this CTA loads
-constexpr ts_u32 kBlockKBytes = 128;                          // one 128-byte swizzle row
+constexpr ts_u32 kBlockKBytes = 16u << TS_SWIZZLE_B;          // one swizzle row: 32, 64 or 128 bytes of K
 constexpr ts_u32 kBlockK      = kBlockKBytes / TS_ELEM_BYTES; // K elements per stage
 constexpr ts_u32 kUmmaKBytes  = 32;                           // K bytes per MMA instruction
-constexpr ts_u32 kNumUmma     = kBlockKBytes / kUmmaKBytes;   // 4 MMAs per stage
+constexpr ts_u32 kNumUmma     = kBlockKBytes / kUmmaKBytes;   // MMAs per stage (4 with 128-byte rows)
 constexpr ts_u32 kStages      = TS_STAGES;
 constexpr ts_u32 kSmemA       = kBlockM * kBlockKBytes;       // 16384
 constexpr ts_u32 kSmemB       = kLoadN * kBlockKBytes;
@@ -220,12 +225,12 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
                         ok = false; break;
                     }
                     ts_tc_fence_after();
-                    const ts_u64 a_desc = ts_smem_desc_sw128(smem_a + s * kSmemA);
-                    const ts_u64 b_desc = ts_smem_desc_sw128(smem_b + s * kSmemB);
+                    const ts_u64 a_desc = ts_smem_desc_kmajor<TS_SWIZZLE_B>(smem_a + s * kSmemA);
+                    const ts_u64 b_desc = ts_smem_desc_kmajor<TS_SWIZZLE_B>(smem_b + s * kSmemB);
                     if (elected) {
 #pragma unroll
                         for (ts_u32 k = 0; k < kNumUmma; ++k) {
-                            // +32 bytes along K inside the 128-byte swizzle row = +2 in the address field
+                            // +32 bytes along K inside the swizzle row = +2 in the address field
                             ts_umma<TS_CTA_GROUP, TS_MMA_KIND>(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc,
                                                                (kb | k) != 0u);
                         }

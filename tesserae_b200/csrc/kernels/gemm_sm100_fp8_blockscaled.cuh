@@ -241,9 +241,6 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
                     const ts_u32 unit = it * kHalves + h;
                     const ts_u32 acc = unit % kNumAcc;
                     const ts_u32 acc_ph = (unit / kNumAcc) & 1u;
-#ifdef TS_TRACE
-                    const long long tr0 = clock64();
-#endif
                     if (!ts_mbar_wait(tmem_empty_bar + 8 * acc, acc_ph ^ 1u)) {
                         if (elected) atomicOr(status, TS_ERR_TIMEOUT_TMEM_EMPTY);
                         ok = false; break;
@@ -253,10 +250,6 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
                         ok = false; break;
                     }
                     ts_tc_fence_after();
-#ifdef TS_TRACE
-                    const long long tr1 = clock64();
-                    long long tr2 = 0;
-#endif
                     const ts_u32 d_tmem = tmem_base + acc * kBufCols;
                     const ts_u64 a_desc = ts_smem_desc_sw128(smem_a + s * kSmemA);
                     const ts_u64 b_desc = ts_smem_desc_sw128(smem_b + s * kSmemB + h * kBRows * 128);
@@ -264,9 +257,6 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
 #pragma unroll
                         for (ts_u32 k = 0; k < kNumUmma; ++k)
                             ts_umma<TS_CTA_GROUP, TS_KIND_F8F6F4>(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, k != 0u);
-#ifdef TS_TRACE
-                        tr2 = clock64();
-#endif
                         // the partial product is complete; the smem stage is free once every issuer's MMAs have read it
                         if (TS_CTA_GROUP == 1) {
                             ts_umma_commit<1>(tmem_full_bar + 8 * acc);
@@ -275,12 +265,6 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
                             ts_umma_commit_pair(tmem_full_bar + 8 * acc, 3);
                             ts_umma_commit_pair(empty_bar + 8 * s, 3);
                         }
-#ifdef TS_TRACE
-                        if (blockIdx.x == 0 && h == 0 && it < 96) {
-                            long long* tr = reinterpret_cast<long long*>(status + 64) + it * 4;
-                            tr[0] = tr0; tr[1] = tr1; tr[2] = tr2; tr[3] = clock64();
-                        }
-#endif
                     }
                     __syncwarp();
                 }
@@ -361,9 +345,6 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
                 const ts_u32 unit = it * kHalves + (half * kWarpCols) / kBufCols;   // the MMA group this warp reads
                 const ts_u32 buf = unit % kNumAcc;
                 const ts_u32 buf_ph = (unit / kNumAcc) & 1u;
-#ifdef TS_TRACE
-                const long long tr0 = clock64();
-#endif
                 const ts_u32 t_row = tmem_base + ((quarter * 32u) << 16) + buf * kBufCols + (half * kWarpCols) % kBufCols;
                 if (!ts_mbar_wait(tmem_full_bar + 8 * buf, buf_ph)) {
                     if (lane == 0) atomicOr(status, TS_ERR_TIMEOUT_TMEM_FULL);
@@ -372,10 +353,6 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
                 ts_tc_fence_after();
                 ts_u32 p0[kLdCols], p1[kLdCols];      // two TMEM load buffers, used in turn
                 ts_tmem_ld(t_row, p0);
-#ifdef TS_TRACE
-                long long tr1 = clock64();
-                long long tr2 = 0;
-#endif
                 // kLdCols columns at a time, two register buffers: the load of the next group is in flight
                 // while the multiply-adds of the current one issue.  The buffer goes back to the tensor core as
                 // soon as its last load has landed, before the last multiply-adds.
@@ -385,38 +362,23 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
                     if (c + 1 < kRounds) {
                         if (c & 1u) ts_tmem_ld(t_row + (c + 1) * kLdCols, p0); else ts_tmem_ld(t_row + (c + 1) * kLdCols, p1);
                     } else {
-#ifdef TS_TRACE
-                        tr1 = clock64();
-#endif
                         ts_tc_fence_before();
                         __syncwarp();
                         if (lane == 0) {
                             if (TS_CTA_GROUP == 2) ts_mbar_arrive_cluster(leader_tmem_empty + 8 * buf);
                             else                   ts_mbar_arrive(tmem_empty_bar + 8 * buf);
                         }
-#ifdef TS_TRACE
-                        tr2 = clock64();
-#endif
                     }
 #pragma unroll
                     for (ts_u32 i = 0; i < kLdCols; ++i)
                         acc[c * kLdCols + i] = fmaf(__uint_as_float((c & 1u) ? p1[i] : p0[i]), s, acc[c * kLdCols + i]);
                 }
-#ifdef TS_TRACE
-                if (blockIdx.x == 0 && warp_id == kFirstPromoWarp && lane == 0 && it < 96) {
-                    long long* tr = reinterpret_cast<long long*>(status + 64) + (96 + it) * 4;
-                    tr[0] = tr0; tr[1] = tr1; tr[2] = tr2; tr[3] = clock64();
-                }
-#endif
                 ++it;
             }
             }
             if (!ok) break;
             // The next tile's first scales: ask for the lines now (no register is tied up while the accumulators
             // are still live), load them after the epilogue.
-#ifdef TS_TRACE
-            const long long te0 = clock64();
-#endif
 #if TS_SCALES_EARLY
             if (has_next) scales_of_tile(m_next, n_next);
 #else
@@ -479,19 +441,10 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
                     ts_bulk_commit();
                 }
             }
-#ifdef TS_TRACE
-            const long long te1 = clock64();
-#endif
 #if !TS_SCALES_EARLY
             if (has_next) scales_of_tile(m_next, n_next);
 #endif
             m_blk = m_next; n_blk = n_next;
-#ifdef TS_TRACE
-            if (blockIdx.x == 0 && warp_id == kFirstPromoWarp && lane == 0 && it / nkb <= 16) {
-                long long* tr = reinterpret_cast<long long*>(status + 64) + (192 + it / nkb) * 4;
-                tr[0] = te0; tr[1] = te1; tr[2] = clock64(); tr[3] = 0;
-            }
-#endif
         }
         if (lane == 0) ts_bulk_wait_all();
         __syncwarp();

@@ -91,14 +91,20 @@ TS_DEV bool ts_mbar_try_wait(ts_u32 bar, ts_u32 parity) {
     return ok != 0;
 }
 // Bounded wait for the phase with the given parity.  Returns false when the cycle budget
-// ran out; the healthy path costs one try_wait.
+// ran out; the healthy path costs one try_wait.  The lanes that call it together get the
+// same answer: once the first try has failed, the outcome of the polling loop is voted on
+// by those lanes, so a barrier that completes just as the budget expires cannot send part
+// of a warp down the error path in front of an aligned instruction.
 TS_DEV bool ts_mbar_wait(ts_u32 bar, ts_u32 parity, ts_i64 budget = TS_WAIT_TIMEOUT_CYCLES) {
     if (ts_mbar_try_wait(bar, parity)) return true;
+    const ts_u32 peers = __activemask();
     const ts_i64 t0 = clock64();
+    bool ok = true;
     while (!ts_mbar_try_wait(bar, parity)) {
-        if (clock64() - t0 > budget) return false;
+        if (clock64() - t0 > budget) { ok = false; break; }
     }
-    return true;
+    __syncwarp(peers);
+    return __all_sync(peers, ok) != 0;
 }
 
 // ---------------------------------------------------------------- TMA
@@ -154,18 +160,23 @@ TS_DEV void ts_tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sy
 TS_DEV void ts_tc_fence_after()  { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 TS_DEV void ts_tmem_wait_ld()    { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// Shared-memory matrix descriptor for a K-major operand tile whose rows are 128 bytes
-// and which TMA wrote with the 128-byte swizzle: 8-row groups are 1024 bytes apart
-// (stride byte offset), the leading byte offset is unused for swizzled K-major tiles
-// (encoded 1), descriptor version 1, layout type 2 (SWIZZLE_128B).  All byte fields
-// drop their four low bits.  The hardware form differs from the reference's sketch
-// (lib/pipeline/smem_desc.ml:38-43), which is kept only as a bit-exact integer function
-// on the host.
-TS_DEV ts_u64 ts_smem_desc_sw128(ts_u32 smem_addr) {
+// Shared-memory matrix descriptor for a K-major operand tile that TMA wrote with Swizzle<B,4,3>
+// (lib/core/swizzle.ml:46-56 picks B from the bytes of K in one tile row: 32, 64 or 128 bytes for
+// B = 1, 2, 3).  Rows are 16 << B bytes, 8-row groups are 8 rows apart (stride byte offset), the
+// leading byte offset is unused for swizzled K-major tiles (encoded 1), descriptor version 1,
+// layout type 6 / 4 / 2 for the 32 / 64 / 128-byte swizzle.  All byte fields drop their four low
+// bits.  The host function of the same content is tesserae_umma_smem_desc.  The hardware form
+// differs from the reference's sketch (lib/pipeline/smem_desc.ml:38-43), which is kept only as a
+// bit-exact integer function on the host.
+template <int SWZ_B> TS_DEV ts_u64 ts_smem_desc_kmajor(ts_u32 smem_addr) {
+    static_assert(SWZ_B >= 1 && SWZ_B <= 3, "K-major operand tiles are swizzled with B in 1..3");
+    constexpr ts_u32 row_bytes = 16u << SWZ_B;
+    constexpr ts_u32 layout = SWZ_B == 3 ? 2u : (SWZ_B == 2 ? 4u : 6u);
     const ts_u32 lo = ((smem_addr & 0x3FFFFu) >> 4) | (1u << 16);
-    const ts_u32 hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+    const ts_u32 hi = ((8u * row_bytes) >> 4) | (1u << 14) | (layout << 29);
     return ((ts_u64)hi << 32) | lo;
 }
+TS_DEV ts_u64 ts_smem_desc_sw128(ts_u32 smem_addr) { return ts_smem_desc_kmajor<3>(smem_addr); }
 // Descriptor for a tile without swizzle whose 8x16-byte core matrices are stored
 // contiguously (128 bytes each): used for the scale-factor copies to TMEM.
 TS_DEV ts_u64 ts_smem_desc_noswizzle(ts_u32 smem_addr, ts_u32 lbo_bytes, ts_u32 sbo_bytes) {

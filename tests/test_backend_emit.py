@@ -43,8 +43,50 @@ def test_emit_rejects_what_the_reference_rejects():
         api.backend_emit(api.KernelSpec(name="k", tile=(128, 192, 64)))
     with pytest.raises(api.TesseraeError, match="UnsupportedArch"):
         api.backend_emit(api.KernelSpec(name="k", arch=api.SM90))
-    with pytest.raises(api.TesseraeError, match="128 bytes"):
-        api.backend_emit(api.KernelSpec(name="k", tile=(128, 256, 32)))
+    with pytest.raises(api.TesseraeError, match="32, 64 or 128 bytes"):
+        api.backend_emit(api.KernelSpec(name="k", tile=(128, 256, 128)))          # 256 bytes of K per row
+    with pytest.raises(api.TesseraeError, match="exactly 128 bytes"):
+        api.backend_emit(api.KernelSpec(name="k", elem=api.F8E4M3, tile=(128, 256, 64), scale_mode=api.SCALE_FP8_BLOCK))
+
+
+def test_operand_swizzle_follows_the_tile():
+    """Swizzle.smem_selector (lib/core/swizzle.ml:46-56) decides the operand tiles' swizzle from tile.k; the
+    emitted kernel is specialised on that B, it is not a constant of the backend."""
+    for tile_k, b in ((64, 3), (32, 2), (16, 1)):
+        spec = api.KernelSpec(name=f"sw{b}", elem=api.BF16, tile=(128, 256, tile_k))
+        assert api.lower(spec).swizzle_b == b
+        out = api.backend_emit(spec)
+        assert f"#define TS_SWIZZLE_B {b}" in out.includes
+        assert f"swizzle=Swizzle<{b},4,3>" in out.includes
+    # and the host-side descriptor builder changes with it: stride byte offset = 8 rows, layout type 2 / 4 / 6
+    lib = N.lib()
+    for b, sbo, layout in ((3, 1024, 2), (2, 512, 4), (1, 256, 6)):
+        d = lib.tesserae_umma_smem_desc(0x4000, b)
+        assert (d >> 32) & 0x3FFF == sbo >> 4 and (d >> 61) & 7 == layout and d & 0x3FFF == 0x4000 >> 4
+
+
+def test_tuning_is_part_of_the_spec():
+    base = api.KernelSpec(name="t0", elem=api.BF16, tile=(128, 256, 64))
+    tuned = api.KernelSpec(name="t0", elem=api.BF16, tile=(128, 256, 64), tuning="GROUP_M=16; STORE_BUFS=3")
+    a, b = api.backend_emit(base).includes, api.backend_emit(tuned).includes
+    assert "#define TS_GROUP_M 8" in a and "#define TS_STORE_BUFS 2" in a
+    assert "#define TS_GROUP_M 16" in b and "#define TS_STORE_BUFS 3" in b
+    with pytest.raises(api.TesseraeError, match="unknown tuning name 'NOPE'"):
+        api.backend_emit(api.KernelSpec(name="t1", tuning="NOPE=1"))
+    with pytest.raises(api.TesseraeError, match="out of range: GROUP_M=0"):
+        api.backend_emit(api.KernelSpec(name="t1", tuning="GROUP_M=0"))
+    with pytest.raises(api.TesseraeError, match="malformed tuning entry"):
+        api.backend_emit(api.KernelSpec(name="t1", tuning="GROUP_M"))
+
+
+def test_no_environment_variable_changes_the_kernel(monkeypatch):
+    spec = api.KernelSpec(name="envfree", elem=api.F8E4M3, tile=(128, 256, 128), scale_mode=api.SCALE_FP8_BLOCK,
+                          out_elem=api.BF16)
+    before = api.backend_emit(spec).full_source
+    for k, v in (("TESSERAE_GROUP_M", "4"), ("TESSERAE_FP8_SPLIT", "0"), ("TESSERAE_FP8_PROMO_WARPS", "16"),
+                 ("TESSERAE_STORE_BUFS", "4"), ("TESSERAE_TRACE", "1")):
+        monkeypatch.setenv(k, v)
+    assert api.backend_emit(spec).full_source == before
 
 
 def test_compile_to_source_and_cubin_with_cache(tmp_path, monkeypatch):

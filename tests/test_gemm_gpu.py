@@ -194,3 +194,21 @@ def test_argument_errors(torch_cuda):
         plan.run(t, t, t, None, 1.0, 16, 16, 12)
     with pytest.raises(api.TesseraeError, match="bias"):
         plan_for(2, api.BF16, 1).run(t, t, t, None, 1.0, 16, 16, 16)
+
+
+@pytest.mark.parametrize("cg", [1, 2])
+@pytest.mark.parametrize("tile_k,swizzle_b", [(32, 2), (16, 1)])
+def test_operand_swizzle_derived_from_tile_k(torch_cuda, cg, tile_k, swizzle_b):
+    """tile.k = 32 / 16 bf16 elements gives 64 / 32-byte rows of K per stage, for which Swizzle.smem_selector
+    (lib/core/swizzle.ml:46-56) derives Swizzle<2,4,3> / Swizzle<1,4,3>: the tensor maps, the shared-memory
+    descriptors and the number of MMAs per stage all follow that B, and the product must not change."""
+    spec = api.KernelSpec(name=f"gemm_bf16_cg{cg}_k{tile_k}", elem=api.BF16, tile=(128, 256, tile_k), cta_group=cg,
+                          out_elem=api.F32)
+    assert api.lower(spec).swizzle_b == swizzle_b
+    plan = api.GemmPlan(spec)
+    for i, (m, n, k) in enumerate([(256, 256, 64), (512, 512, 512), (200, 264, 72), (129, 8, 520)]):
+        p = O.make_bf16_problem(m, n, k, seed=900 + i)
+        got = run_gpu(torch_cuda, plan, p, m, n, k, api.F32)
+        e = O.rel_error(got, O.gemm_f32(p["a"], p["b"]))
+        assert e["max_rel"] <= TOL_F32_OUT, (cg, tile_k, m, n, k, e)
+    plan.close()

@@ -13,6 +13,14 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
+def _free_port() -> str:
+    """A rendezvous port nobody holds right now (the machine is shared; a fixed port can be taken)."""
+    import socket
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return str(s.getsockname()[1])
+
+
 def test_fused_exchange_two_gpus():
     import torch
     if not torch.cuda.is_available():
@@ -21,7 +29,7 @@ def test_fused_exchange_two_gpus():
         pytest.skip("needs 2 GPUs")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
-           "127.0.0.1", "--master-port", "29533", os.path.join(HERE, "helpers", "ksplit_fused_worker.py")]
+           "127.0.0.1", "--master-port", _free_port(), os.path.join(HERE, "helpers", "ksplit_fused_worker.py")]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     line = [ln for ln in r.stdout.splitlines() if ln.startswith("RESULT ")][-1]
@@ -41,7 +49,7 @@ def test_nccl_through_the_c_abi_two_gpus():
         pytest.skip("needs 2 GPUs")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
-           "127.0.0.1", "--master-port", "29534", os.path.join(HERE, "helpers", "nccl_capi_worker.py")]
+           "127.0.0.1", "--master-port", _free_port(), os.path.join(HERE, "helpers", "nccl_capi_worker.py")]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     line = [ln for ln in r.stdout.splitlines() if ln.startswith("RESULT ")][-1]
