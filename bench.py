@@ -1,19 +1,19 @@
 #!/usr/bin/env python
 """Benchmark of the dense GEMM hot path on N B200s of one node.
 
-    python bench.py --gpus N --steps K --warmup W [--workload NAME] [--impl reference]
+    python bench.py --gpus N --steps K --warmup W [--workload NAME] [--sub-configs all|none] [--impl reference]
 
 One step = one pass of the hot path over the workload: one GEMM launch per GPU (plus, for the
 K-split workload, the reduce-scatter of the fp32 partials and the sum + bf16 cast).  Rank 0
 prints ONE JSON line.  `value` is whole-job TFLOP/s with operands resident in HBM; `e2e` is the
-same metric with HOST buffers (host->device copies of the operands and the device->host copy
-of C inside the timed region).  `roofline` bounds the kernel by the measured cuBLAS bf16
-throughput of this pool (MEASURED_PEAKS.json) scaled by the nominal ratio of the dtype's tensor
-rate to bf16's; `cpu_baseline` times the CPU oracle (the reference has no CPU GEMM of its own)
-on a bounded sample of the same workload.
+same metric through the C-ABI call that takes HOST buffers (host->device copies of the operands
+and the device->host copy of C inside the timed region).  `roofline` bounds the kernel by the
+measured cuBLAS bf16 throughput of this pool (MEASURED_PEAKS.json) scaled by the nominal ratio of
+the dtype's tensor rate to bf16's; `cpu_baseline` times the CPU oracle (the reference has no CPU
+GEMM of its own) on a bounded sample of the same workload.
 
 Workloads (BASELINE.json configs):
-  bf16_8192_bias   configs[1]  default.  At N > 1 the N-split of C = A . B^T over the output
+  bf16_8192_bias   configs[1]  headline.  At N > 1 the N-split of C = A . B^T over the output
                                columns, 8192 columns per GPU, no collective: weak scaling.
   bf16_512         configs[0]  plumbing check.
   fp8_block        configs[2]  8192 x 14336 x 4096, N-split of the fixed problem: strong scaling.
@@ -21,6 +21,10 @@ Workloads (BASELINE.json configs):
   bf16_ksplit      configs[4]  8192 x 8192 x 131072, K-split + reduce-scatter (fused or NCCL) of the fp32
                                partials + bf16 cast: strong scaling; compute and communication
                                reported separately.
+The default run measures the headline workload and then, in the same process and at the same N,
+fp8_block, nvfp4 and bf16_ksplit (with both exchanges at N > 1); their records go into the line's
+`configs` object.  Operand sources are drawn on the GPU from a seeded Philox generator (the host
+generator needs minutes for 10^9 values) and quantised by the library's own GPU quantisers.
 """
 from __future__ import annotations
 
@@ -50,6 +54,7 @@ WORKLOADS = {
     "bf16_ksplit": dict(kind="ksplit", dtype="bf16", m=8192, n=8192, k=131072, seed=4, dist="uniform", scale=0.5,
                         bias=False, out="bf16", shard="k_strong", tile="256x256x64 per CTA pair"),
 }
+SUB_CONFIGS = ["fp8_block", "nvfp4", "bf16_ksplit"]
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel, from the ncu
 # captures summarised under profiles/; None where no capture exists.
 TRAFFIC_BYTES = {"bf16_8192_bias": 1.2437e9, "fp8_block": 4.737e8, "nvfp4": 2.2376e9}
@@ -61,9 +66,9 @@ def measured_peaks():
 
 
 class ClockSampler(threading.Thread):
-    """Samples SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
+    """Samples SM clock and throttle reasons through NVML (read-only) while a timed region runs."""
 
-    def __init__(self, index: int, period_s: float = 0.02):
+    def __init__(self, index: int, period_s: float = 0.001):
         super().__init__(daemon=True)
         self.index, self.period, self.samples, self.reasons, self.max_mhz = index, period_s, [], set(), None
         self._halt = threading.Event()
@@ -103,8 +108,8 @@ class ClockSampler(threading.Thread):
         if not self.samples:
             return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": 0}
         s = sorted(self.samples)
-        return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
-                "samples": len(s)}
+        return {"sm_mhz": s[len(s) // 2], "sm_min_mhz": s[0], "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s), "period_ms": self.period * 1e3}
 
 
 # --------------------------------------------------------------------------- CPU side (oracle)
@@ -198,24 +203,29 @@ class Workload:
             self.k = w["k"] // world
         self.stream = torch.cuda.current_stream().cuda_stream
         self.launches_per_step = 1
+        self.e2e_api = "tesserae_gemm_run_host"
         getattr(self, "_setup_" + w["kind"])()
 
     def _draw(self, shape, seed):
+        """Seeded fp32 source on this GPU (Philox: the same values on every rank for a given seed)."""
         t, w = self.torch, self.w
-        g = t.Generator().manual_seed(seed)
+        g = t.Generator(device=self.dev).manual_seed(seed)
         if w["dist"] == "normal":
-            return t.randn(shape, generator=g, dtype=t.float32) * w["scale"]
-        return (t.rand(shape, generator=g, dtype=t.float32) * 2 - 1) * w["scale"]
+            return t.randn(shape, generator=g, dtype=t.float32, device=self.dev) * w["scale"]
+        return (t.rand(shape, generator=g, dtype=t.float32, device=self.dev) * 2 - 1) * w["scale"]
+
+    def _pin(self, x):
+        return x.cpu().pin_memory()
 
     def _setup_bf16(self):
         t, w, api = self.torch, self.w, self.api
-        self.a_host = self._draw((self.m, self.k), w["seed"]).to(t.bfloat16).pin_memory()
-        self.b_host = self._draw((self.n, self.k), w["seed"] + 1000 + self.rank).to(t.bfloat16).pin_memory()
-        self.bias_host = (t.randn(self.n, generator=t.Generator().manual_seed(w["seed"] + 2000 + self.rank)) * 0.1
-                          ).to(t.bfloat16).pin_memory() if w["bias"] else None
+        self.a = self._draw((self.m, self.k), w["seed"]).to(t.bfloat16)
+        self.b = self._draw((self.n, self.k), w["seed"] + 1000 + self.rank).to(t.bfloat16)
+        self.bias = (t.randn(self.n, generator=t.Generator(device=self.dev).manual_seed(w["seed"] + 2000 + self.rank),
+                             device=self.dev) * 0.1).to(t.bfloat16) if w["bias"] else None
+        self.a_host, self.b_host = self._pin(self.a), self._pin(self.b)
+        self.bias_host = self._pin(self.bias) if w["bias"] else None
         self.c_host = t.empty((self.m, self.n), dtype=t.bfloat16).pin_memory()
-        self.a, self.b = self.a_host.to(self.dev), self.b_host.to(self.dev)
-        self.bias = self.bias_host.to(self.dev) if w["bias"] else None
         self.c = t.empty((self.m, self.n), dtype=t.bfloat16, device=self.dev)
         self.plan = api.GemmPlan(api.KernelSpec(name=f"gemm_bf16_cg2_bf16_b{int(w['bias'])}", elem=api.BF16,
                                                 tile=(128, 256, 64), cta_group=2, out_elem=api.BF16, has_bias=int(w["bias"])))
@@ -224,74 +234,69 @@ class Workload:
                                                    self.m, self.n, self.k)
         self.h2d = self.a_host.numel() * 2 + self.b_host.numel() * 2 + (self.n * 2 if w["bias"] else 0)
         self.d2h = self.c_host.numel() * 2
-        self.ref_ab = lambda: (self.a_host.float().numpy(), self.b_host.float().numpy(),
-                               None if self.bias_host is None else self.bias_host.float().numpy())
 
     def _setup_fp8(self):
-        t, np, O, api, w = self.torch, self.np, self.O, self.api, self.w
+        t, api, w = self.torch, self.api, self.w
         n0 = self.rank * self.n
-        a_src = self._draw((self.m, self.k), w["seed"]).numpy()
-        b_src = self._draw((w["n"], self.k), w["seed"] + 1000).numpy()[n0:n0 + self.n]
-        qa, sa = O.quantize_fp8_rows_1x128(a_src)
-        qb, sb = O.quantize_fp8_blocks_128x128(b_src)
-        self._deq = (O.dequantize_fp8_rows(qa, sa), O.dequantize_fp8_blocks(qb, sb))
-        dev = lambda x: t.from_numpy(np.ascontiguousarray(x)).to(self.dev)
-        self.a, self.b, self.sa, self.sb = dev(qa), dev(qb), dev(sa), dev(sb)
+        src = self._draw((self.m, self.k), w["seed"])
+        self.a = t.empty((self.m, self.k), dtype=t.uint8, device=self.dev)
+        self.sa = t.empty((self.m, self.k // 128), dtype=t.float32, device=self.dev)
+        api.quantize_fp8_rows(src, self.a, self.sa, self.m, self.k, stream=self.stream)
+        src = self._draw((w["n"], self.k), w["seed"] + 1000)[n0:n0 + self.n].contiguous()   # the shard's rows of the one B
+        self.b = t.empty((self.n, self.k), dtype=t.uint8, device=self.dev)
+        self.sb = t.empty(((self.n + 127) // 128, self.k // 128), dtype=t.float32, device=self.dev)
+        api.quantize_fp8_blocks(src, self.b, self.sb, self.n, self.k, stream=self.stream)
+        del src
+        self.ga = self.gb = 1.0
         self.c = t.empty((self.m, self.n), dtype=t.bfloat16, device=self.dev)
         self.plan = api.GemmPlan(api.KernelSpec(name="gemm_fp8blk_cg2_n256", elem=api.F8E4M3, tile=(128, 256, 128),
                                                 cta_group=2, out_elem=api.BF16, scale_mode=api.SCALE_FP8_BLOCK))
-        self.step = lambda: self.plan.run_scaled(self.a, self.b, self.c, self.sa, self.sb, None, 1.0, self.m, self.n,
-                                                 self.k, stream=self.stream)
-        self._host_pack(qa, qb, [sa, sb])
-        self.ref_ab = lambda: (self._deq[0], self._deq[1], None)
+        self._finish_scaled()
 
     def _setup_nvfp4(self):
-        t, np, O, api, w = self.torch, self.np, self.O, self.api, self.w
+        t, api, w = self.torch, self.api, self.w
         n0 = self.rank * self.n
-        a_src = self._draw((self.m, self.k), w["seed"]).numpy()
-        b_all = self._draw((w["n"], self.k), w["seed"] + 1000).numpy()
-        qa, sa, ga = O.quantize_nvfp4(a_src)
-        qb, sb, gb = O.quantize_nvfp4(b_all)              # one per-tensor scale for the whole B, not per shard
-        qb, sb = qb[n0:n0 + self.n], sb[n0:n0 + self.n]
-        del b_all
-        self._deq = (O.dequantize_nvfp4(qa, sa, ga), O.dequantize_nvfp4(qb, sb, gb))
-        dev = lambda x: t.from_numpy(np.ascontiguousarray(x)).to(self.dev)
-        pa, pb, ca, cb = O.pack_e2m1(qa), O.pack_e2m1(qb), O.nvfp4_scale_chunks(sa), O.nvfp4_scale_chunks(sb)
-        self.a, self.b, self.sa, self.sb, self.ga, self.gb = dev(pa), dev(pb), dev(ca), dev(cb), float(ga), float(gb)
+        ws4 = t.zeros(4, dtype=t.uint8, device=self.dev)
+
+        def quant(rows, seed):
+            src = self._draw((rows, self.k), seed)
+            q = t.empty((rows, self.k // 2), dtype=t.uint8, device=self.dev)
+            sf = t.zeros((api.nvfp4_scale_bytes(rows, self.k),), dtype=t.uint8, device=self.dev)
+            g = api.quantize_nvfp4(src, q, sf, ws4, rows, self.k, stream=self.stream)
+            return q, sf, g
+        self.a, self.sa, self.ga = quant(self.m, w["seed"])
+        qb, sfb, self.gb = quant(w["n"], w["seed"] + 1000)         # one per-tensor scale for the whole B, not per shard
+        per_row_block = (self.k // 64) * 512                       # scale bytes of one 128-row block
+        self.b = qb[n0:n0 + self.n].contiguous()
+        self.sb = sfb[(n0 // 128) * per_row_block:((n0 + self.n + 127) // 128) * per_row_block].contiguous()
+        del qb, sfb
         self.c = t.empty((self.m, self.n), dtype=t.bfloat16, device=self.dev)
         self.plan = api.GemmPlan(api.KernelSpec(name="gemm_nvfp4_cg2_n256", elem=api.F4E2M1, tile=(128, 256, 256),
                                                 cta_group=2, out_elem=api.BF16, scale_mode=api.SCALE_NVFP4))
+        self._finish_scaled()
+
+    def _finish_scaled(self):
+        """Device step through tesserae_gemm_run_scaled; end-to-end step through tesserae_gemm_run_scaled_host with
+        pinned host copies of the quantised operands and scale tables (they go up, C comes back, inside the call)."""
+        t = self.torch
         self.step = lambda: self.plan.run_scaled(self.a, self.b, self.c, self.sa, self.sb, None, 1.0, self.m, self.n,
                                                  self.k, stream=self.stream, global_a=self.ga, global_b=self.gb)
-        self._host_pack(pa, pb, [ca, cb])
-        self.ref_ab = lambda: (self._deq[0], self._deq[1], None)
-
-    def _host_pack(self, qa, qb, scales):
-        """Pinned host copies for the end-to-end leg of the scaled kernels: operands and scale tables go up,
-        C comes back; the launch itself is the device-pointer C-ABI entry point."""
-        t, np = self.torch, self.np
-        pin = lambda x: t.from_numpy(np.ascontiguousarray(x)).pin_memory()
-        self.h_in = [pin(qa), pin(qb)] + [pin(s) for s in scales]
-        self.d_in = [self.a, self.b, self.sa, self.sb]
+        self.h_in = [self._pin(x) for x in (self.a, self.b, self.sa, self.sb)]
         self.c_host = t.empty((self.m, self.n), dtype=t.bfloat16).pin_memory()
         self.h2d = sum(x.numel() * x.element_size() for x in self.h_in)
         self.d2h = self.c_host.numel() * 2
-
-        def e2e():
-            for h, d in zip(self.h_in, self.d_in):
-                d.copy_(h, non_blocking=True)
-            self.step()
-            self.c_host.copy_(self.c, non_blocking=True)
-            t.cuda.current_stream().synchronize()
-        self.e2e_step = e2e
+        self.e2e_api = "tesserae_gemm_run_scaled_host"
+        self.e2e_step = lambda: self.plan.run_scaled_host(self.h_in[0], self.h_in[1], self.c_host, self.h_in[2], self.h_in[3],
+                                                          None, 1.0, self.m, self.n, self.k, global_a=self.ga, global_b=self.gb)
 
     def _setup_ksplit(self):
         t, api, w = self.torch, self.api, self.w
         import torch.distributed as dist
-        # K slice of this rank: pre-sharded, contiguous M x K/G and N x K/G buffers
-        self.a_host = self._draw((self.m, self.k), w["seed"] + 10 * self.rank).to(t.bfloat16).pin_memory()
-        self.b_host = self._draw((self.n, self.k), w["seed"] + 1000 + 10 * self.rank).to(t.bfloat16).pin_memory()
-        self.a, self.b = self.a_host.to(self.dev), self.b_host.to(self.dev)
+        # K slice of this rank of the one seeded A and B: contiguous M x K/G and N x K/G buffers
+        k0 = self.rank * self.k
+        self.a = self._draw((self.m, w["k"]), w["seed"])[:, k0:k0 + self.k].to(t.bfloat16).contiguous()
+        self.b = self._draw((self.n, w["k"]), w["seed"] + 1000)[:, k0:k0 + self.k].to(t.bfloat16).contiguous()
+        self.a_host, self.b_host = self._pin(self.a), self._pin(self.b)
         self.partial = t.empty((self.m, self.n), dtype=t.float32, device=self.dev)       # scratch: fp32 partial C
         rows = self.m // self.world
         self.mine = t.empty((rows, self.n), dtype=t.float32, device=self.dev) if self.world > 1 else self.partial
@@ -368,9 +373,9 @@ class Workload:
             self.c_host.copy_(self.c, non_blocking=True)
             t.cuda.current_stream().synchronize()
         self.e2e_step = e2e
+        self.e2e_api = "harness copies around the device-pointer K-split entry points (no host-buffer K-split call exists)"
         self.h2d = self.a_host.numel() * 2 + self.b_host.numel() * 2
         self.d2h = self.c_host.numel() * 2
-        self.ref_ab = None
 
     def _check_ksplit(self):
         """Sampled entries of every owner's rows: each rank's fp64 partial over its own K slice, summed over the
@@ -381,7 +386,8 @@ class Workload:
         local = [0, rows_per // 2, rows_per - 1]
         rows = [g * rows_per + r for g in range(self.world) for r in local]
         cols = list(range(0, self.n, 61))
-        part = O.gemm_f64_entries(self.a_host.float().numpy(), self.b_host.float().numpy(), rows, cols, 1.0, None)
+        part = O.gemm_f64_entries(self.a[rows].float().cpu().numpy(), self.b[cols].float().cpu().numpy(),
+                                  list(range(len(rows))), list(range(len(cols))), 1.0, None)
         tot = t.from_numpy(np.ascontiguousarray(part)).to(self.dev)
         if self.world > 1:
             dist.all_reduce(tot, op=dist.ReduceOp.SUM)
@@ -390,6 +396,30 @@ class Workload:
         rms = float(np.sqrt(np.mean(want ** 2)))
         return float(np.max(np.abs(got - want) / np.maximum(np.abs(want), rms / 128)))
 
+    def _sampled_operands(self, rows, cols):
+        """fp32 values (oracle arithmetic) of rows `rows` of A and rows `cols` of B, and the sampled bias."""
+        np, O, t, w = self.np, self.O, self.torch, self.w
+        idx = lambda v: t.as_tensor(v, device=self.dev)
+        if w["kind"] == "bf16":
+            bias = self.bias[idx(cols)].float().cpu().numpy() if self.bias is not None else None
+            return self.a[idx(rows)].float().cpu().numpy(), self.b[idx(cols)].float().cpu().numpy(), bias
+        if w["kind"] == "fp8":
+            a = O.dequantize_fp8_rows(self.a[idx(rows)].cpu().numpy(), self.sa[idx(rows)].cpu().numpy())
+            qb = O.e4m3_bits_to_f32(self.b[idx(cols)].cpu().numpy())
+            sb = self.sb[idx([c // 128 for c in cols])].cpu().numpy()
+            b = (qb.reshape(len(cols), self.k // 128, 128) * sb[:, :, None]).reshape(len(cols), self.k).astype(np.float32)
+            return a, b, None
+        kg = self.k // 64
+
+        def nv(q, sf, g, rr):
+            rr = np.asarray(rr)
+            codes = O.unpack_e2m1(q[idx(rr)].cpu().numpy())
+            blocks = sf.view(-1, kg, 512)[idx(rr // 128)].cpu().numpy()
+            off = ((rr % 128) % 32) * 16 + ((rr % 128) // 32) * 4
+            s_bits = np.stack([blocks[i, :, off[i]:off[i] + 4].reshape(-1) for i in range(len(rr))])
+            return O.dequantize_nvfp4(codes, s_bits, g)
+        return nv(self.a, self.sa, self.ga, rows), nv(self.b, self.sb, self.gb, cols), None
+
     def flops_total(self):
         w = self.w
         if w["shard"] == "n_weak":
@@ -397,53 +427,44 @@ class Workload:
         return 2.0 * w["m"] * w["n"] * w["k"]
 
     def check(self):
-        """Sampled entries of this rank's output against the oracle in fp64 (untimed)."""
+        """Sampled entries of this rank's output against the oracle in fp64 (untimed).  The operands are read back
+        from the device as the bytes the kernel saw and turned into values by the oracle's own (de)quantisers."""
         if self.w["kind"] == "ksplit":
             return self._check_ksplit()
         np, O = self.np, self.O
-        a, b, bias = self.ref_ab()
         rows = [0, self.m // 2, self.m - 1]
         cols = list(range(0, self.n, 61))
-        want = O.gemm_f64_entries(a, b, rows, cols, 1.0, bias)
+        a, b, bias = self._sampled_operands(rows, cols)
+        want = O.gemm_f64_entries(a, b, list(range(len(rows))), list(range(len(cols))), 1.0, bias)
         got = self.c[rows][:, cols].float().cpu().numpy()
         rms = float(np.sqrt(np.mean(want ** 2)))
         return float(np.max(np.abs(got - want) / np.maximum(np.abs(want), rms / 128)))
 
+    def close(self):
+        try:
+            self.plan.close()
+        except Exception:
+            pass
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--workload", default="bf16_8192_bias", choices=sorted(WORKLOADS))
-    ap.add_argument("--impl", default="tesserae_b200", choices=["tesserae_b200", "reference"])
-    ap.add_argument("--e2e-steps", type=int, default=5)
-    ap.add_argument("--cpu-budget", type=float, default=12.0, help="seconds of CPU work per cpu_baseline sample")
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--ksplit-exchange", default="fused", choices=["fused", "nccl"],
-                    help="K-split at 2+ GPUs: scatter fused into the GEMM's stores over peer memory, or NCCL reduce-scatter")
-    args = ap.parse_args()
-    w = WORKLOADS[args.workload]
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    args.warmup = max(args.warmup, 3)
 
-    if args.impl == "reference":
-        run_reference(args, w, rank)
-        return 0
+def roofline_peak(w, elapsed_ms):
+    peaks = measured_peaks()
+    ratio = NOMINAL_PEAK_TFLOPS[w["dtype"]] / NOMINAL_PEAK_TFLOPS["bf16"]
+    if peaks:
+        sustained = elapsed_ms >= 100.0       # back-to-back launches for 0.1 s or more run under the power cap
+        base = peaks["bf16_tflops_sustained"] if sustained else peaks["bf16_tflops"]
+        note = (f"measured: cuBLAS bf16 8192^3 {'sustained' if sustained else 'burst'} figure of this pool "
+                f"({base} TFLOP/s)" + (f" x {ratio:g} (nominal {w['dtype']}/bf16 tensor rate)" if ratio != 1 else ""))
+        return base * ratio, note
+    return FALLBACK_PEAK_TFLOPS * ratio, "fallback: no MEASURED_PEAKS.json"
 
+
+def measure(name, w, rank, local_rank, world, dev, args, exchange="fused", extras=False):
+    """Builds the workload, runs warm-up + the timed steps + burst + (K-split) split + end-to-end legs and the
+    oracle check, reduces over the ranks (max) and returns the record (on every rank) plus the live workload."""
     import torch
     import torch.distributed as dist
-
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA GPU: tesserae_b200 has no CPU path")
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-
-    wl = Workload(args.workload, w, rank, world, dev, exchange=args.ksplit_exchange)
+    wl = Workload(name, w, rank, world, dev, exchange=exchange)
 
     def sync_all():
         torch.cuda.synchronize()
@@ -462,6 +483,7 @@ def main():
         wl.step()
     e1.record()
     sync_all()
+    clocks = sampler.stop()
     elapsed_ms = e0.elapsed_time(e1)
     status = wl.plan.status()
 
@@ -493,56 +515,216 @@ def main():
         wl.e2e_step()
     torch.cuda.synchronize()
     e2e_ms = 1e3 * (time.perf_counter() - t0)
-    clocks = sampler.stop()
+    wl.step()                                     # the check reads the device-resident output of a plain step
+    torch.cuda.synchronize()
     max_rel = wl.check()
 
     vals = [elapsed_ms, e2e_ms, float(status), max_rel, min(burst_ms)] + (split or [0.0, 0.0])
-    t = torch.tensor(vals, dtype=torch.float64, device=dev)
+    tt = torch.tensor(vals, dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+    elapsed_ms, e2e_ms, status, max_rel, burst, gemm_ms, comm_ms = tt.tolist()
+
+    flops_step = wl.flops_total()
+    ms_per_step = elapsed_ms / args.steps
+    value = flops_step / (ms_per_step * 1e-3) / 1e12
+    peak, peak_note = roofline_peak(w, elapsed_ms)
+    kernel_ms = gemm_ms if split else ms_per_step
+    kernel_tflops = flops_step / world / (kernel_ms * 1e-3) / 1e12
+    nominal = NOMINAL_PEAK_TFLOPS[w["dtype"]]
+    rec = {
+        "value": value, "unit": "TFLOP/s", "ms_per_step": ms_per_step, "steps": args.steps, "warmup": args.warmup,
+        "scaling": scaling_of(w), "dtype": w["dtype"], "config": workload_config(name, w, world, exchange),
+        "pct_of_nominal_dense_peak": 100.0 * value / world / nominal,
+        "burst": {"value": flops_step / (burst * 1e-3) / 1e12, "unit": "TFLOP/s",
+                  "note": "best of 10 single steps, each after an idle gap and two untimed steps",
+                  "pct_of_nominal_dense_peak": 100.0 * flops_step / world / (burst * 1e-3) / 1e12 / nominal},
+        "roofline": {"bound": "tensor", "achieved": kernel_tflops, "peak": peak, "unit": "TFLOP/s",
+                     "frac": kernel_tflops / peak, "traffic": TRAFFIC_BYTES.get(name),
+                     "peak_source": peak_note, "kernel": wl.plan.spec.name,
+                     "algorithmic_flops_per_launch": flops_step / world},
+        "e2e": {"value": flops_step / (e2e_ms / args.e2e_steps * 1e-3) / 1e12, "unit": "TFLOP/s",
+                "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h, "steps": args.e2e_steps,
+                "ms_per_step": e2e_ms / args.e2e_steps, "api": wl.e2e_api,
+                "per_rank_copy_gbs": (wl.h2d + wl.d2h) / (e2e_ms / args.e2e_steps * 1e-3) / 1e9},
+        "gpu_launches": args.steps * wl.launches_per_step,
+        "clocks": clocks,
+        "kernel_status": int(status), "max_rel_err_vs_oracle_sample": max_rel,
+    }
+    if split:
+        rec["ksplit"] = {"exchange": exchange if world > 1 else "none", "gemm_ms": gemm_ms,
+                         "reduce_scatter_plus_cast_ms": comm_ms,
+                         "exposed_after_gemm_ms": ms_per_step - gemm_ms}
+    return rec, wl, sync_all
+
+
+def pcie_probe(wl, world, dev):
+    """Achieved host->device and device->host GB/s of this rank's link with all ranks copying at once (what bounds
+    the end-to-end leg): one plain copy of A up and of C back, CUDA events; min / max over the ranks."""
+    import torch
+    import torch.distributed as dist
+    src, dst = wl.a_host, wl.c_host
+    d_in = torch.empty_like(src, device=dev)
+    d_out = torch.empty_like(dst, device=dev)
+    out = []
+    for h, d, up in ((src, d_in, True), (dst, d_out, False)):
+        for _ in range(2):
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            if world > 1:
+                dist.barrier()
+            ev0.record()
+            (d.copy_(h, non_blocking=True) if up else h.copy_(d, non_blocking=True))
+            ev1.record()
+            torch.cuda.synchronize()
+        out.append(h.numel() * h.element_size() / (ev0.elapsed_time(ev1) * 1e-3) / 1e9)
+    t = torch.tensor([out[0], out[1], -out[0], -out[1]], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    elapsed_ms, e2e_ms, status, max_rel, burst, gemm_ms, comm_ms = t.tolist()
+    mx0, mx1, mn0, mn1 = t.tolist()
+    return {"h2d_gbs_per_rank": {"min": -mn0, "max": mx0}, "d2h_gbs_per_rank": {"min": -mn1, "max": mx1},
+            "note": "all ranks copy at the same time; a per-rank figure that falls as N grows means the ranks share a "
+                    "host-side limit (root complex / host DRAM), not their own PCIe link"}
+
+
+def sustained_leg(fn, local_rank, seconds, flops_per_call):
+    """Back-to-back calls for about `seconds`, NVML sampled every 2 ms: TFLOP/s, median SM MHz and the product
+    time x clock (SM cycles per call), which separates idle cycles from a lower clock."""
+    import torch
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(); fn(); e1.record(); torch.cuda.synchronize()
+    n = max(20, int(seconds * 1e3 / max(e0.elapsed_time(e1), 1e-3)))
+    sampler = ClockSampler(local_rank, period_s=0.002)
+    sampler.start()
+    e0.record()
+    for _ in range(n):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1) / n
+    rec = {"value": flops_per_call / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "calls": n, "seconds": ms * n * 1e-3,
+           "ms_per_call": ms, "clocks": clocks}
+    if clocks.get("sm_mhz"):
+        rec["sm_cycles_per_call"] = ms * 1e-3 * clocks["sm_mhz"] * 1e6
+    return rec
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--workload", default="bf16_8192_bias", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="tesserae_b200", choices=["tesserae_b200", "reference"])
+    ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--cpu-budget", type=float, default=12.0, help="seconds of CPU work per cpu_baseline sample")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sub-configs", default=None, choices=["all", "none"],
+                    help="also measure fp8_block, nvfp4 and bf16_ksplit in the same process (default: all for the "
+                         "headline workload, none otherwise)")
+    ap.add_argument("--sustained-seconds", type=float, default=1.0)
+    ap.add_argument("--ksplit-exchange", default="fused", choices=["fused", "nccl"],
+                    help="K-split at 2+ GPUs: scatter fused into the GEMM's stores over peer memory, or NCCL reduce-scatter")
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    args.warmup = max(args.warmup, 3)
+    if args.sub_configs is None:
+        args.sub_configs = "all" if args.workload == "bf16_8192_bias" else "none"
+
+    if args.impl == "reference":
+        run_reference(args, w, rank)
+        return 0
+
+    import torch
+    import torch.distributed as dist
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA GPU: tesserae_b200 has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    rec, wl, sync_all = measure(args.workload, w, rank, local_rank, world, dev, args, exchange=args.ksplit_exchange)
+    line = {"metric": "gemm_tflops", "value": rec["value"], "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": rec["ms_per_step"], "higher_is_better": True, "scaling": rec["scaling"],
+            "vs_baseline": None, "dtype": w["dtype"],
+            "data": "synthetic (seeded Philox draws on the GPU; FP8 / NVFP4 operands made by the library's GPU quantisers)"}
+    line.update({k: v for k, v in rec.items() if k not in ("value", "unit", "ms_per_step", "steps", "warmup", "scaling", "dtype")})
+
+    # ---- where the end-to-end leg's time goes: achieved copy rates per rank with all ranks copying
+    if w["kind"] != "ksplit":
+        line["e2e"]["copy_probe"] = pcie_probe(wl, world, dev)
+
+    # ---- the headline kernel against cuBLAS in the same process, both regimes, with the clock seen
+    if w["kind"] == "bf16" and w["m"] >= 4096:
+        flops_one = 2.0 * wl.m * wl.n * wl.k
+        bt = wl.b.t()
+        cub = lambda: torch.matmul(wl.a, bt)
+        burst = []
+        for _ in range(10):
+            time.sleep(0.02)
+            b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            cub(); cub()
+            b0.record(); cub(); b1.record()
+            torch.cuda.synchronize()
+            burst.append(b0.elapsed_time(b1))
+        sync_all()
+        ours_sus = sustained_leg(wl.step, local_rank, args.sustained_seconds, flops_one)
+        sync_all()
+        cub_sus = sustained_leg(cub, local_rank, args.sustained_seconds, flops_one)
+        sync_all()
+        line["sustained"] = ours_sus
+        line["cublas_same_box"] = {"burst": flops_one / (min(burst) * 1e-3) / 1e12, "sustained": cub_sus["value"],
+                                   "unit": "TFLOP/s per GPU", "sustained_detail": cub_sus,
+                                   "note": "torch.matmul(A, B^T) bf16 on this rank's operands, no bias, same regimes as "
+                                           "`burst` and `sustained` of this line"}
+        line["vs_cublas_same_box"] = {"burst": (line["burst"]["value"] / world) / line["cublas_same_box"]["burst"],
+                                      "sustained": ours_sus["value"] / cub_sus["value"]}
+    wl.close()
+    del wl
+    torch.cuda.empty_cache()
+
+    # ---- the other BASELINE configs, same process, same N
+    if args.sub_configs == "all":
+        subs = {}
+        for name in SUB_CONFIGS:
+            if name == args.workload:
+                continue
+            sw = WORKLOADS[name]
+            try:
+                srec, swl, _ = measure(name, sw, rank, local_rank, world, dev, args, exchange="fused")
+                if sw["kind"] == "ksplit" and world > 1:
+                    fused_c = swl.c.clone()
+                    swl.close(); del swl
+                    torch.cuda.empty_cache()
+                    nrec, nwl, _ = measure(name, sw, rank, local_rank, world, dev, args, exchange="nccl")
+                    same = torch.equal(fused_c.view(torch.int16), nwl.c.view(torch.int16))
+                    diff = (fused_c.float() - nwl.c.float()).abs().max()
+                    flags = torch.tensor([0.0 if same else 1.0, float(diff)], dtype=torch.float64, device=dev)
+                    dist.all_reduce(flags, op=dist.ReduceOp.MAX)
+                    srec["nccl"] = {k: nrec[k] for k in ("value", "ms_per_step", "ksplit", "max_rel_err_vs_oracle_sample",
+                                                         "kernel_status", "pct_of_nominal_dense_peak")}
+                    srec["fused_equals_nccl"] = flags[0].item() == 0.0
+                    srec["fused_vs_nccl_max_abs_diff"] = flags[1].item()
+                    srec["fused_vs_nccl_note"] = ("both exchanges sum the same fp32 partials; the fused one adds the source "
+                                                  "ranks' slots in rank order, NCCL in its ring order, so beyond 2 ranks the "
+                                                  "bf16 results may differ in the last place")
+                    swl = nwl
+                subs[name] = srec
+                swl.close(); del swl
+            except Exception as exc:                       # a sub-record must not take the headline down
+                subs[name] = {"error": f"{type(exc).__name__}: {exc}"}
+            torch.cuda.empty_cache()
+        line["configs"] = subs
 
     if rank == 0:
-        flops_step = wl.flops_total()
-        ms_per_step = elapsed_ms / args.steps
-        value = flops_step / (ms_per_step * 1e-3) / 1e12
-        per_gpu = value / world
-        peaks = measured_peaks()
-        ratio = NOMINAL_PEAK_TFLOPS[w["dtype"]] / NOMINAL_PEAK_TFLOPS["bf16"]
-        if peaks:
-            sustained = elapsed_ms >= 100.0       # back-to-back launches for 0.1 s or more run under the power cap
-            base = peaks["bf16_tflops_sustained"] if sustained else peaks["bf16_tflops"]
-            peak = base * ratio
-            peak_note = (f"measured: cuBLAS bf16 8192^3 {'sustained' if sustained else 'burst'} figure of this pool "
-                         f"({base} TFLOP/s)" + (f" x {ratio:g} (nominal {w['dtype']}/bf16 tensor rate)" if ratio != 1 else ""))
-        else:
-            peak, peak_note = FALLBACK_PEAK_TFLOPS * ratio, "fallback: no MEASURED_PEAKS.json"
-        kernel_ms = gemm_ms if split else ms_per_step
-        kernel_tflops = flops_step / world / (kernel_ms * 1e-3) / 1e12
-        line = {
-            "metric": "gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": scaling_of(w),
-            "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic (seeded, generated on the host)",
-            "config": workload_config(args.workload, w, world, args.ksplit_exchange),
-            "pct_of_nominal_dense_peak": 100.0 * per_gpu / NOMINAL_PEAK_TFLOPS[w["dtype"]],
-            "burst": {"value": flops_step / (burst * 1e-3) / 1e12, "unit": "TFLOP/s",
-                      "note": "best of 10 single steps, each after an idle gap and two untimed steps",
-                      "pct_of_nominal_dense_peak": 100.0 * flops_step / world / (burst * 1e-3) / 1e12 / NOMINAL_PEAK_TFLOPS[w["dtype"]]},
-            "roofline": {"bound": "tensor", "achieved": kernel_tflops, "peak": peak, "unit": "TFLOP/s",
-                         "frac": kernel_tflops / peak, "traffic": TRAFFIC_BYTES.get(args.workload),
-                         "peak_source": peak_note, "kernel": wl.plan.spec.name,
-                         "algorithmic_flops_per_launch": flops_step / world},
-            "e2e": {"value": flops_step / (e2e_ms / args.e2e_steps * 1e-3) / 1e12, "unit": "TFLOP/s",
-                    "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h, "steps": args.e2e_steps,
-                    "ms_per_step": e2e_ms / args.e2e_steps},
-            "gpu_launches": args.steps * wl.launches_per_step,
-            "clocks": clocks,
-            "kernel_status": int(status), "max_rel_err_vs_oracle_sample": max_rel,
-        }
-        if split:
-            line["ksplit"] = {"exchange": args.ksplit_exchange if world > 1 else "none", "gemm_ms": gemm_ms,
-                              "reduce_scatter_plus_cast_ms": comm_ms,
-                              "exposed_after_gemm_ms": ms_per_step - gemm_ms}
         if not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_gemm_sample(w, budget_s=args.cpu_budget)[0]
         print(json.dumps(line), flush=True)

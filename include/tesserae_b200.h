@@ -127,6 +127,98 @@ int64_t tesserae_tile_io_expect_tx(int elem, int strategy, int bm, int bn, int b
 int64_t tesserae_predicate_count_valid(const int64_t* shape, const int64_t* bounds, int n);
 int tesserae_predicate_residue(const int64_t* shape, const int64_t* bounds, int n, int64_t* out);
 
+/* ------------------------------------------------------------------ Memspace, atoms, tiled atoms, Tile_op
+ * Plain-integer restatements of lib/core/memspace.ml, lib/atoms/{mma_atom,copy_atom,tiled_mma,tiled_copy}.ml and
+ * lib/pipeline/tile_op.ml.  The reference's phantom types (arch, element, memory space) become integer codes. */
+/* Memspace.space (lib/core/memspace.ml:8-12) */
+enum { TESSERAE_SPACE_GLOBAL = 0, TESSERAE_SPACE_SHARED = 1, TESSERAE_SPACE_REGISTER = 2, TESSERAE_SPACE_TENSOR = 3 };
+/* Memspace.can_transfer (lib/core/memspace.ml:26-47): 1 / 0 */
+int tesserae_memspace_can_transfer(int src_space, int dst_space);
+/* Memspace.name (lib/core/memspace.ml:14-20) */
+const char* tesserae_memspace_name(int space);
+
+/* Mma_atom.t (lib/atoms/mma_atom.ml:17-28); `arch` is a TESSERAE_SM* code, the types are element codes */
+enum { TESSERAE_ROW_MAJOR = 0, TESSERAE_COL_MAJOR = 1 };
+enum {  /* the reference's atom constructors, lib/atoms/mma_atom.ml:32-112, in file order */
+    TESSERAE_MMA_SM80_16x8x8_F32F16F16F32 = 0, TESSERAE_MMA_SM80_16x8x16_F32F16F16F32 = 1,
+    TESSERAE_MMA_SM80_16x8x16_F32BF16BF16F32 = 2, TESSERAE_MMA_SM80_16x8x32_S32S8S8S32 = 3,
+    TESSERAE_MMA_SM90_64x64x16_F32F16F16F32 = 4, TESSERAE_MMA_SM90_64x128x16_F32F16F16F32 = 5,
+    TESSERAE_MMA_SM90_64x64x16_F32BF16BF16F32 = 6, TESSERAE_MMA_SM100_64x64x16_F32F16F16F32 = 7,
+    TESSERAE_MMA_SM100_128x128x16_F32F16F16F32 = 8, TESSERAE_MMA_SM100_64x64x32_S32S8S8S32 = 9
+};
+typedef struct tesserae_mma_atom {
+    int arch, m, n, k;
+    int a_type, b_type, c_type, d_type;
+    int a_major, b_major;
+} tesserae_mma_atom;
+int tesserae_mma_atom_make(int which, int a_major, int b_major, tesserae_mma_atom* out);
+/* Mma_atom.thread_count / is_wgmma / emit_cpp (lib/atoms/mma_atom.ml:118-156) */
+int tesserae_mma_atom_thread_count(const tesserae_mma_atom* atom);
+int tesserae_mma_atom_is_wgmma(const tesserae_mma_atom* atom);
+int tesserae_mma_atom_emit_cpp(const tesserae_mma_atom* atom, char* buf, size_t buf_size);
+
+/* Copy_atom.kind (lib/atoms/copy_atom.ml:4-12).  TMA_LOAD_PAIR is the reference's fifth kind (its SM100
+ * cluster-wide TMA load), which this backend lowers to the per-CTA loads of a CTA pair. */
+enum {
+    TESSERAE_COPY_ASYNC_GLOBAL = 0, TESSERAE_COPY_ASYNC_CACHED = 1, TESSERAE_COPY_TMA_LOAD = 2,
+    TESSERAE_COPY_TMA_STORE = 3, TESSERAE_COPY_TMA_LOAD_PAIR = 4, TESSERAE_COPY_LDMATRIX = 5,
+    TESSERAE_COPY_LDMATRIX_TRANS = 6, TESSERAE_COPY_UNIVERSAL = 7
+};
+typedef struct tesserae_copy_atom { int kind, src_space, dst_space, elem, vec_width, bulk_bytes; } tesserae_copy_atom;
+/* The reference's constructors (lib/atoms/copy_atom.ml:23-104); src/dst spaces are read for UNIVERSAL only. */
+int tesserae_copy_atom_make(int kind, int elem, int src_space, int dst_space, tesserae_copy_atom* out);
+/* Copy_atom.is_async / is_tma / requires_mbar / emit_cpp (lib/atoms/copy_atom.ml:106-137) */
+int tesserae_copy_atom_is_async(const tesserae_copy_atom* atom);
+int tesserae_copy_atom_is_tma(const tesserae_copy_atom* atom);
+int tesserae_copy_atom_requires_mbar(const tesserae_copy_atom* atom);
+int tesserae_copy_atom_emit_cpp(const tesserae_copy_atom* atom, char* buf, size_t buf_size);
+
+/* Tiled_mma (lib/atoms/tiled_mma.ml:12-53).  The reference reads only the sizes of the thread and warp
+ * layouts; partition_a/b/c are the sizes of the `n:1` fragments it returns.  Fails with the reference's
+ * message when the thread layout does not match the atom. */
+typedef struct tesserae_tiled_mma {
+    int64_t thread_count, warp_count;
+    int64_t tile_m, tile_n, tile_k;                 /* tile_shape_mnk */
+    int64_t partition_a, partition_b, partition_c;
+} tesserae_tiled_mma;
+int tesserae_tiled_mma_make(const tesserae_mma_atom* atom, int64_t thread_layout_size, int64_t warp_layout_size,
+                            int64_t tiler_m, int64_t tiler_n, tesserae_tiled_mma* out);
+/* Tiled_copy (lib/atoms/tiled_copy.ml:10-50) */
+typedef struct tesserae_tiled_copy {
+    int64_t thread_count, elements_per_thread, tile_size;
+    int is_tma, requires_mbar;
+} tesserae_tiled_copy;
+int tesserae_tiled_copy_make(const tesserae_copy_atom* atom, int64_t thread_layout_size, int64_t val_layout_size,
+                             tesserae_tiled_copy* out);
+/* Tiled_copy.partition_src / partition_dst (lib/atoms/tiled_copy.ml:38-50): Algebra.flat_divide by the thread
+ * count, "across" mode kept.  Writes one mode; returns 1 (the mode count) or -1. */
+int tesserae_tiled_copy_partition(int64_t thread_count, const int64_t* shape, const int64_t* stride, int n,
+                                  int64_t* out_shape, int64_t* out_stride);
+
+/* Tile_op.t (lib/pipeline/tile_op.ml:9-16): a tiled MMA plus where its accumulator lives. */
+enum { TESSERAE_ACCUM_REGISTERS = 0, TESSERAE_ACCUM_TENSOR_MEM = 1 };
+typedef struct tesserae_tile_op {
+    tesserae_mma_atom atom;
+    int64_t thread_layout_size, warp_layout_size, tiler_m, tiler_n;
+    int accum_loc;                                  /* TESSERAE_ACCUM_* */
+    int has_tmem, tmem_cta_group, tmem_cols, tmem_rows;
+    int double_buf;
+} tesserae_tile_op;
+/* Tile_op.make's checks (lib/pipeline/tile_op.ml:18-37): "TensorMem requires a tmem descriptor" */
+int tesserae_tile_op_check(const tesserae_tile_op* op);
+/* Tile_op.is_tmem / is_wgmma / accum_elems_per_thread (lib/pipeline/tile_op.ml:39-50) */
+int tesserae_tile_op_is_tmem(const tesserae_tile_op* op);
+int tesserae_tile_op_is_wgmma(const tesserae_tile_op* op);
+int64_t tesserae_tile_op_accum_elems_per_thread(const tesserae_tile_op* op);
+/* Tile_op.emit_* (lib/pipeline/tile_op.ml:52-107), the reference's instruction text.  `what` selects the
+ * emitter; arg0/arg1/flag are (a_desc, b_desc, enable_accum) for MMA, (mbar_var, -, cta_mask) for COMMIT,
+ * (var name, -, -) for the rest.  The text is descriptive: the kernels of this library are built from the
+ * working PTX wrappers, not from these strings. */
+enum { TESSERAE_TILE_OP_MMA = 0, TESSERAE_TILE_OP_COMMIT = 1, TESSERAE_TILE_OP_ACCUM_DECL = 2,
+       TESSERAE_TILE_OP_TMEM_ALLOC = 3, TESSERAE_TILE_OP_TMEM_DEALLOC = 4 };
+int tesserae_tile_op_emit(const tesserae_tile_op* op, int what, const char* arg0, const char* arg1, int flag,
+                          char* buf, size_t buf_size);
+
 /* ------------------------------------------------------------------ kernel spec -> descriptor */
 /* Kernel_ast.kernel (lib/kernel/kernel_ast.ml:64-72).  `args` and `body` of the reference
  * record are DSL statements that its lowering never reads (lib/kernel/lower.ml:61-83), so
@@ -147,8 +239,13 @@ typedef struct tesserae_kernel_spec {
      * The kernel a plan runs is a function of its spec alone; nothing is read from the environment.  Names:
      *   GROUP_M=1..64          M-tiles per raster group of the persistent tile order
      *   STORE_BUFS=2..4        dense kernel: staging buffers per epilogue warp
+     *   L2_HINT=0..7           dense kernel: L2 eviction hints, bit 1 = A tiles evict_last, 2 = B tiles evict_first,
+     *                          4 = stores of C evict_first
      *   FP8_PROMO_WARPS=8|16   block-scaled FP8: promotion warps
      *   FP8_SPLIT=0|1          block-scaled FP8: one MMA chain per tile width / per 128 columns
+     *   FP8_FMA2=0|1           block-scaled FP8: scalar / packed-pair promotion multiply-adds
+     *   FP8_XPIPE=0|1          block-scaled FP8: load each K block's partial product after / before the previous
+     *                          block's last multiply-adds
      * An unknown name or a value out of range fails with IncompatibleTile. */
     const char* tuning;
 } tesserae_kernel_spec;
@@ -415,6 +512,11 @@ int tesserae_wait_selftest(int64_t budget_cycles, uint32_t* status_out, int64_t*
  * the device, runs, copies C back, all inside the call.  Synchronous. */
 int tesserae_gemm_run_host(tesserae_gemm_plan* plan, const void* a, const void* b, void* c, const void* bias,
                            float alpha, int64_t m, int64_t n, int64_t k);
+/* The block-scaled call with host buffers: A, B, both scale tables (in `scales`, HOST pointers here) and the bias
+ * go up, C comes back, inside the call; same chunked pipeline as tesserae_gemm_run_host.  Synchronous. */
+int tesserae_gemm_run_scaled_host(tesserae_gemm_plan* plan, const void* a, const void* b, void* c,
+                                  const tesserae_gemm_scales* scales, const void* bias,
+                                  float alpha, int64_t m, int64_t n, int64_t k);
 /* Runtime.run (lib/runtime/runtime.ml:15-75): fp32 host arrays in, fp32 host array out;
  * A and B are rounded to the spec's element type on the host (the reference uploads fp32
  * bits unconverted, lib/runtime/gpu_buffer.ml:32-40, which its kernels then misread). */

@@ -293,6 +293,199 @@ def tmem_buf_col_offset(buf: int) -> int:
     return buf * 256
 
 
+def tmem_alloc_ptx(t: dict, smem_var: str) -> str:           # lib/pipeline/tmem.ml:72-75
+    return f"tcgen05.alloc.cta_group::{t['cta_group']}.sync.aligned.shared::cta.b32 [{smem_var}], {t['num_cols']};"
+
+
+def tmem_dealloc_ptx(t: dict, taddr_var: str) -> str:        # lib/pipeline/tmem.ml:77-80
+    return f"tcgen05.dealloc.cta_group::{t['cta_group']}.sync.aligned.b32 {taddr_var}, {t['num_cols']};"
+
+
+def tmem_commit_ptx(t: dict, mbar_var: str) -> str:          # lib/pipeline/tmem.ml:91-94
+    return f"tcgen05.commit.cta_group::{t['cta_group']}.mbarrier::arrive::one.shared::cluster.b64 [{mbar_var}];"
+
+
+def tmem_commit_mask_ptx(t: dict, mbar_var: str, cta_mask: int) -> str:    # lib/pipeline/tmem.ml:115-118
+    return (f"tcgen05.commit.cta_group::{t['cta_group']}.mbarrier::arrive::one.multicast::cluster.shared::cluster.b64 "
+            f"[{mbar_var}], {cta_mask};")
+
+
+# --------------------------------------------------------------------------- Memspace (lib/core/memspace.ml:14-47)
+SPACES = ("global", "shared", "register", "tensor")
+
+
+def memspace_can_transfer(src: str, dst: str) -> bool:
+    if src == dst:
+        return True
+    return (src, dst) in {("global", "shared"), ("global", "register"), ("shared", "register"), ("register", "shared"),
+                          ("register", "global")}
+
+
+# --------------------------------------------------------------------------- Mma_atom (lib/atoms/mma_atom.ml:31-157)
+_ELEM_TAG = {"f32": "F32", "f16": "F16", "bf16": "BF16", "s8": "S8", "s32": "S32"}
+MMA_ATOMS = {   # constructor name -> (arch, m, n, k, a/b type, c/d type), in the order of the reference file
+    "sm80_16x8x8_f32f16f16f32": ("SM80", 16, 8, 8, "f16", "f32"),
+    "sm80_16x8x16_f32f16f16f32": ("SM80", 16, 8, 16, "f16", "f32"),
+    "sm80_16x8x16_f32bf16bf16f32": ("SM80", 16, 8, 16, "bf16", "f32"),
+    "sm80_16x8x32_s32s8s8s32": ("SM80", 16, 8, 32, "s8", "s32"),
+    "sm90_64x64x16_f32f16f16f32": ("SM90", 64, 64, 16, "f16", "f32"),
+    "sm90_64x128x16_f32f16f16f32": ("SM90", 64, 128, 16, "f16", "f32"),
+    "sm90_64x64x16_f32bf16bf16f32": ("SM90", 64, 64, 16, "bf16", "f32"),
+    "sm100_64x64x16_f32f16f16f32": ("SM100", 64, 64, 16, "f16", "f32"),
+    "sm100_128x128x16_f32f16f16f32": ("SM100", 128, 128, 16, "f16", "f32"),
+    "sm100_64x64x32_s32s8s8s32": ("SM100", 64, 64, 32, "s8", "s32"),
+}
+
+
+def mma_atom(name: str, a_major: str = "ColMajor", b_major: str = "RowMajor") -> dict:
+    arch, m, n, k, ab, cd = MMA_ATOMS[name]
+    return {"arch": arch, "m": m, "n": n, "k": k, "a_type": ab, "b_type": ab, "c_type": cd, "d_type": cd,
+            "a_major": a_major, "b_major": b_major}
+
+
+def mma_atom_thread_count(a: dict) -> int:
+    return 32 if a["arch"] == "SM80" else 128
+
+
+def mma_atom_is_wgmma(a: dict) -> bool:
+    return a["arch"] != "SM80"
+
+
+def mma_atom_emit_cpp(a: dict) -> str:
+    mc = lambda mj: "T" if mj == "ColMajor" else "N"
+    return (f"{a['arch']}_{a['m']}x{a['n']}x{a['k']}_{_ELEM_TAG[a['d_type']]}{_ELEM_TAG[a['a_type']]}"
+            f"{_ELEM_TAG[a['b_type']]}{_ELEM_TAG[a['c_type']]}_{mc(a['a_major'])}{mc(a['b_major'])}")
+
+
+# --------------------------------------------------------------------------- Copy_atom (lib/atoms/copy_atom.ml:23-137)
+# "TmaLoadPair" is this build's name for the reference's fifth kind (its SM100 cluster-wide TMA load).
+def copy_atom(kind: str, elem: str, src: str = "global", dst: str = "shared") -> dict:
+    bw = ELEM_BYTES[elem]
+    if kind in ("AsyncCopyGlobal", "AsyncCopyCached"):
+        return {"kind": kind, "src": "global", "dst": "shared", "elem": elem, "bulk_bytes": 16, "vec_width": 16 // bw}
+    if kind in ("Ldmatrix", "LdmatrixTrans"):
+        return {"kind": kind, "src": "shared", "dst": "register", "elem": elem, "bulk_bytes": 32, "vec_width": 8}
+    if kind in ("TmaLoad", "TmaLoadPair"):
+        return {"kind": kind, "src": "global", "dst": "shared", "elem": elem, "bulk_bytes": 128, "vec_width": 128 // bw}
+    if kind == "TmaStore":
+        return {"kind": kind, "src": "shared", "dst": "global", "elem": elem, "bulk_bytes": 128, "vec_width": 128 // bw}
+    if kind == "UniversalCopy":
+        return {"kind": kind, "src": src, "dst": dst, "elem": elem, "bulk_bytes": bw, "vec_width": 1}
+    raise ValueError("unknown copy atom kind")
+
+
+def copy_atom_is_tma(a: dict) -> bool:
+    return a["kind"] in ("TmaLoad", "TmaStore", "TmaLoadPair")
+
+
+def copy_atom_is_async(a: dict) -> bool:
+    return a["kind"] in ("AsyncCopyGlobal", "AsyncCopyCached") or copy_atom_is_tma(a)
+
+
+def copy_atom_requires_mbar(a: dict) -> bool:
+    return copy_atom_is_tma(a)
+
+
+def copy_atom_emit_cpp(a: dict) -> str:
+    fixed = {"AsyncCopyGlobal": "SM80_CP_ASYNC_CACHEGLOBAL<cute::uint128_t>", "AsyncCopyCached": "SM80_CP_ASYNC_CACHEALL<cute::uint128_t>",
+             "TmaLoad": "SM90_TMA_LOAD", "TmaStore": "SM90_TMA_STORE", "TmaLoadPair": "SM100_TMA_LOAD_" + "MULTI" + "CAST",
+             "Ldmatrix": "SM80_U32x4_LDSM_N", "LdmatrixTrans": "SM80_U16x8_LDSM_T"}
+    return fixed.get(a["kind"]) or f"UniversalCopy<{ELEM_CPP[a['elem']]}>"
+
+
+# --------------------------------------------------------------------------- Tiled_mma (lib/atoms/tiled_mma.ml:12-53)
+def tiled_mma_make(atom: dict, thread_layout: Layout, warp_layout: Layout, tiler_mn) -> dict:
+    if layout_size(thread_layout) != mma_atom_thread_count(atom):
+        raise ValueError("thread_layout size does not match atom thread count")
+    return {"atom": atom, "thread_layout": thread_layout, "warp_layout": warp_layout, "tiler_mn": tiler_mn}
+
+
+def tiled_mma_thread_count(t: dict) -> int:
+    return layout_size(t["thread_layout"]) * layout_size(t["warp_layout"])
+
+
+def tiled_mma_warp_count(t: dict) -> int:
+    return layout_size(t["warp_layout"])
+
+
+def tiled_mma_tile_shape_mnk(t: dict):
+    mn = flatten(t["tiler_mn"])
+    if len(mn) != 2:
+        raise ValueError("tiler_mn must represent exactly two dimensions (M and N)")
+    return (mn[0], mn[1], t["atom"]["k"])
+
+
+def tiled_mma_partition(t: dict, which: str) -> Layout:
+    a = t["atom"]
+    total = {"a": a["m"] * a["k"], "b": a["n"] * a["k"], "c": a["m"] * a["n"]}[which]
+    return Layout(total // layout_size(t["thread_layout"]), 1)
+
+
+# --------------------------------------------------------------------------- Tiled_copy (lib/atoms/tiled_copy.ml:10-50)
+def tiled_copy_make(atom: dict, thread_layout: Layout, val_layout: Layout) -> dict:
+    if layout_size(val_layout) != atom["vec_width"]:
+        raise ValueError("val_layout size does not match atom vec_width")
+    if layout_size(thread_layout) <= 0:
+        raise ValueError("thread_layout size must be positive")
+    return {"atom": atom, "thread_layout": thread_layout, "val_layout": val_layout}
+
+
+def tiled_copy_tile_size(t: dict) -> int:
+    return layout_size(t["thread_layout"]) * layout_size(t["val_layout"])
+
+
+def tiled_copy_partition(t: dict, layout: Layout) -> Layout:
+    d = flat_divide(layout, layout_size(t["thread_layout"]))
+    return Layout(d.shape[1], d.stride[1])
+
+
+# --------------------------------------------------------------------------- Tile_op (lib/pipeline/tile_op.ml:18-107)
+def tile_op_make(tiled_mma: dict, accum_loc: str, tmem: dict | None = None, double_buf: bool = False) -> dict:
+    if accum_loc == "TensorMem" and tmem is None:
+        raise ValueError("TensorMem requires a tmem descriptor")
+    return {"tiled_mma": tiled_mma, "accum_loc": accum_loc, "tmem": tmem, "double_buf": double_buf}
+
+
+def tile_op_is_tmem(t: dict) -> bool:
+    return t["accum_loc"] == "TensorMem"
+
+
+def tile_op_is_wgmma(t: dict) -> bool:
+    return mma_atom_is_wgmma(t["tiled_mma"]["atom"])
+
+
+def tile_op_accum_elems_per_thread(t: dict) -> int:
+    return layout_size(tiled_mma_partition(t["tiled_mma"], "c"))
+
+
+def tile_op_emit_mma(t: dict, a_desc: str, b_desc: str, enable_accum: bool) -> str:
+    if t["accum_loc"] == "Registers":
+        return f"mma.sync.aligned.{mma_atom_emit_cpp(t['tiled_mma']['atom'])} acc, {a_desc}, {b_desc}, acc;"
+    cg = t["tmem"]["cta_group"] if t["tmem"] else 1
+    return f"tcgen05.mma.cta_group::{cg}.kind::mxf16 [tmem_addr], {a_desc}, {b_desc}, [i_desc], {1 if enable_accum else 0};"
+
+
+def tile_op_emit_commit(t: dict, mbar_var: str, cta_mask: int) -> str:
+    if t["accum_loc"] == "Registers" or t["tmem"] is None:
+        return ""
+    return tmem_commit_mask_ptx(t["tmem"], mbar_var, cta_mask) if cta_mask > 1 else tmem_commit_ptx(t["tmem"], mbar_var)
+
+
+def tile_op_emit_accum_decl(t: dict, var: str) -> str:
+    if t["accum_loc"] == "TensorMem":
+        return ""
+    n = tile_op_accum_elems_per_thread(t)
+    return f"float {var}[{n}] = {{{', '.join(['0.0f'] * n)}}};"
+
+
+def tile_op_emit_tmem_alloc(t: dict, smem_var: str) -> str:
+    return tmem_alloc_ptx(t["tmem"], smem_var) if t["tmem"] else ""
+
+
+def tile_op_emit_tmem_dealloc(t: dict, taddr_var: str) -> str:
+    return tmem_dealloc_ptx(t["tmem"], taddr_var) if t["tmem"] else ""
+
+
 # --------------------------------------------------------------------------- Smem_desc (lib/pipeline/smem_desc.ml:17-43)
 def smem_desc_encode(base: int, leading: int, stride: int, sw_bits: int) -> int:
     # OCaml native ints are 63 bits wide: the value is reported as that bit pattern (unsigned).

@@ -53,6 +53,30 @@ class GemmScalesC(C.Structure):
     _fields_ = [("scale_a", C.c_void_p), ("scale_b", C.c_void_p), ("global_a", C.c_float), ("global_b", C.c_float)]
 
 
+class MmaAtomC(C.Structure):
+    _fields_ = [(f, C.c_int) for f in ("arch", "m", "n", "k", "a_type", "b_type", "c_type", "d_type", "a_major", "b_major")]
+
+
+class CopyAtomC(C.Structure):
+    _fields_ = [(f, C.c_int) for f in ("kind", "src_space", "dst_space", "elem", "vec_width", "bulk_bytes")]
+
+
+class TiledMmaC(C.Structure):
+    _fields_ = [(f, C.c_int64) for f in ("thread_count", "warp_count", "tile_m", "tile_n", "tile_k", "partition_a",
+                                         "partition_b", "partition_c")]
+
+
+class TiledCopyC(C.Structure):
+    _fields_ = [("thread_count", C.c_int64), ("elements_per_thread", C.c_int64), ("tile_size", C.c_int64),
+                ("is_tma", C.c_int), ("requires_mbar", C.c_int)]
+
+
+class TileOpC(C.Structure):
+    _fields_ = [("atom", MmaAtomC), ("thread_layout_size", C.c_int64), ("warp_layout_size", C.c_int64),
+                ("tiler_m", C.c_int64), ("tiler_n", C.c_int64), ("accum_loc", C.c_int), ("has_tmem", C.c_int),
+                ("tmem_cta_group", C.c_int), ("tmem_cols", C.c_int), ("tmem_rows", C.c_int), ("double_buf", C.c_int)]
+
+
 class LaunchArgC(C.Structure):
     _fields_ = [("data", C.c_void_p), ("size", C.c_size_t)]
 
@@ -98,6 +122,25 @@ SIGNATURES = {
     "tesserae_tile_io_expect_tx": (C.c_int64, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "tesserae_predicate_count_valid": (C.c_int64, [_I64P, _I64P, C.c_int]),
     "tesserae_predicate_residue": (C.c_int, [_I64P, _I64P, C.c_int, _I64P]),
+    "tesserae_memspace_can_transfer": (C.c_int, [C.c_int, C.c_int]),
+    "tesserae_memspace_name": (C.c_char_p, [C.c_int]),
+    "tesserae_mma_atom_make": (C.c_int, [C.c_int, C.c_int, C.c_int, C.POINTER(MmaAtomC)]),
+    "tesserae_mma_atom_thread_count": (C.c_int, [C.POINTER(MmaAtomC)]),
+    "tesserae_mma_atom_is_wgmma": (C.c_int, [C.POINTER(MmaAtomC)]),
+    "tesserae_mma_atom_emit_cpp": (C.c_int, [C.POINTER(MmaAtomC), C.c_char_p, C.c_size_t]),
+    "tesserae_copy_atom_make": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(CopyAtomC)]),
+    "tesserae_copy_atom_is_async": (C.c_int, [C.POINTER(CopyAtomC)]),
+    "tesserae_copy_atom_is_tma": (C.c_int, [C.POINTER(CopyAtomC)]),
+    "tesserae_copy_atom_requires_mbar": (C.c_int, [C.POINTER(CopyAtomC)]),
+    "tesserae_copy_atom_emit_cpp": (C.c_int, [C.POINTER(CopyAtomC), C.c_char_p, C.c_size_t]),
+    "tesserae_tiled_mma_make": (C.c_int, [C.POINTER(MmaAtomC), C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.POINTER(TiledMmaC)]),
+    "tesserae_tiled_copy_make": (C.c_int, [C.POINTER(CopyAtomC), C.c_int64, C.c_int64, C.POINTER(TiledCopyC)]),
+    "tesserae_tiled_copy_partition": (C.c_int, [C.c_int64, _I64P, _I64P, C.c_int, _I64P, _I64P]),
+    "tesserae_tile_op_check": (C.c_int, [C.POINTER(TileOpC)]),
+    "tesserae_tile_op_is_tmem": (C.c_int, [C.POINTER(TileOpC)]),
+    "tesserae_tile_op_is_wgmma": (C.c_int, [C.POINTER(TileOpC)]),
+    "tesserae_tile_op_accum_elems_per_thread": (C.c_int64, [C.POINTER(TileOpC)]),
+    "tesserae_tile_op_emit": (C.c_int, [C.POINTER(TileOpC), C.c_int, C.c_char_p, C.c_char_p, C.c_int, C.c_char_p, C.c_size_t]),
     "tesserae_lower": (C.c_int, [C.POINTER(KernelSpecC), C.POINTER(KernelDescC)]),
     "tesserae_kernel_desc_validate": (C.c_int, [C.POINTER(KernelDescC)]),
     "tesserae_kernel_desc_arithmetic_intensity": (C.c_double, [C.POINTER(KernelDescC)]),
@@ -173,6 +216,8 @@ SIGNATURES = {
     "tesserae_gemm_status": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint32)]),
     "tesserae_gemm_run_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_float,
                                          C.c_int64, C.c_int64, C.c_int64]),
+    "tesserae_gemm_run_scaled_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(GemmScalesC),
+                                                C.c_void_p, C.c_float, C.c_int64, C.c_int64, C.c_int64]),
     "tesserae_runtime_run": (C.c_int, [C.POINTER(KernelSpecC), C.c_int64, C.c_int64, C.c_int64,
                                        C.POINTER(C.c_float), C.POINTER(C.c_float), C.POINTER(C.c_float)]),
     "tesserae_runtime_is_available": (C.c_int, []),

@@ -179,6 +179,13 @@ class GemmPlan:
         check(N.lib().tesserae_gemm_run_host(self._h, _ptr(a), _ptr(b), _ptr(c), _ptr(bias), alpha, m, n, k),
               "gemm_run_host")
 
+    def run_scaled_host(self, a, b, c, scale_a, scale_b, bias=None, alpha: float = 1.0, m=None, n=None, k=None,
+                        global_a: float = 1.0, global_b: float = 1.0) -> None:
+        """Block-scaled GEMM with host buffers (operands, scale tables, bias up; C back) inside the call."""
+        sc = N.GemmScalesC(_ptr(scale_a), _ptr(scale_b), global_a, global_b)
+        check(N.lib().tesserae_gemm_run_scaled_host(self._h, _ptr(a), _ptr(b), _ptr(c), C.byref(sc), _ptr(bias), alpha,
+                                                    m, n, k), "gemm_run_scaled_host")
+
     def status(self) -> int:
         s = C.c_uint32()
         check(N.lib().tesserae_gemm_status(self._h, C.byref(s)), "gemm_status")
@@ -390,3 +397,135 @@ def layout_flat_divide(shape, stride, divisor: int):
 def layout_logical_divide(shape, stride, tile_shape):
     t, _ = _arr(tile_shape)
     return _unary(N.lib().tesserae_layout_logical_divide, shape, stride, t, nout=2 * len(list(shape)) + 1)
+
+
+# ---------------------------------------------------------------- Memspace, atoms, tiled atoms, Tile_op
+SPACES = {"global": 0, "shared": 1, "register": 2, "tensor": 3}
+ELEMS = {"f16": F16, "bf16": BF16, "f32": F32, "s8": S8, "s32": S32}
+MAJORS = {"RowMajor": 0, "ColMajor": 1}
+MMA_ATOM_IDS = {name: i for i, name in enumerate([
+    "sm80_16x8x8_f32f16f16f32", "sm80_16x8x16_f32f16f16f32", "sm80_16x8x16_f32bf16bf16f32", "sm80_16x8x32_s32s8s8s32",
+    "sm90_64x64x16_f32f16f16f32", "sm90_64x128x16_f32f16f16f32", "sm90_64x64x16_f32bf16bf16f32",
+    "sm100_64x64x16_f32f16f16f32", "sm100_128x128x16_f32f16f16f32", "sm100_64x64x32_s32s8s8s32"])}
+COPY_KINDS = {"AsyncCopyGlobal": 0, "AsyncCopyCached": 1, "TmaLoad": 2, "TmaStore": 3, "TmaLoadPair": 4, "Ldmatrix": 5,
+              "LdmatrixTrans": 6, "UniversalCopy": 7}
+TILE_OP_TEXT = {"mma": 0, "commit": 1, "accum_decl": 2, "tmem_alloc": 3, "tmem_dealloc": 4}
+
+
+def _text(fn, *args) -> str:
+    buf = C.create_string_buffer(4096)
+    if fn(*args, buf, 4096) != 0:
+        raise ValueError(N.last_error())
+    return buf.value.decode()
+
+
+def memspace_can_transfer(src: str, dst: str) -> bool:
+    """Memspace.can_transfer (lib/core/memspace.ml:26-47)."""
+    return bool(N.lib().tesserae_memspace_can_transfer(SPACES[src], SPACES[dst]))
+
+
+def memspace_name(space: str) -> str:
+    return N.lib().tesserae_memspace_name(SPACES[space]).decode()
+
+
+def mma_atom(name: str, a_major: str = "ColMajor", b_major: str = "RowMajor") -> N.MmaAtomC:
+    """One of the reference's Mma_atom constructors (lib/atoms/mma_atom.ml:32-112)."""
+    a = N.MmaAtomC()
+    if N.lib().tesserae_mma_atom_make(MMA_ATOM_IDS[name], MAJORS[a_major], MAJORS[b_major], C.byref(a)) != 0:
+        raise ValueError(N.last_error())
+    return a
+
+
+def mma_atom_thread_count(a) -> int:
+    return N.lib().tesserae_mma_atom_thread_count(C.byref(a))
+
+
+def mma_atom_is_wgmma(a) -> bool:
+    return bool(N.lib().tesserae_mma_atom_is_wgmma(C.byref(a)))
+
+
+def mma_atom_emit_cpp(a) -> str:
+    return _text(N.lib().tesserae_mma_atom_emit_cpp, C.byref(a))
+
+
+def copy_atom(kind: str, elem: str, src: str = "global", dst: str = "shared") -> N.CopyAtomC:
+    """One of the reference's Copy_atom constructors (lib/atoms/copy_atom.ml:23-104)."""
+    a = N.CopyAtomC()
+    if N.lib().tesserae_copy_atom_make(COPY_KINDS[kind], ELEMS[elem], SPACES[src], SPACES[dst], C.byref(a)) != 0:
+        raise ValueError(N.last_error())
+    return a
+
+
+def copy_atom_is_async(a) -> bool:
+    return bool(N.lib().tesserae_copy_atom_is_async(C.byref(a)))
+
+
+def copy_atom_is_tma(a) -> bool:
+    return bool(N.lib().tesserae_copy_atom_is_tma(C.byref(a)))
+
+
+def copy_atom_requires_mbar(a) -> bool:
+    return bool(N.lib().tesserae_copy_atom_requires_mbar(C.byref(a)))
+
+
+def copy_atom_emit_cpp(a) -> str:
+    return _text(N.lib().tesserae_copy_atom_emit_cpp, C.byref(a))
+
+
+def tiled_mma(atom, thread_layout_size: int, warp_layout_size: int, tiler_m: int, tiler_n: int) -> N.TiledMmaC:
+    """Tiled_mma.make and its derived numbers (lib/atoms/tiled_mma.ml:12-53)."""
+    t = N.TiledMmaC()
+    if N.lib().tesserae_tiled_mma_make(C.byref(atom), thread_layout_size, warp_layout_size, tiler_m, tiler_n, C.byref(t)) != 0:
+        raise ValueError(N.last_error())
+    return t
+
+
+def tiled_copy(atom, thread_layout_size: int, val_layout_size: int) -> N.TiledCopyC:
+    """Tiled_copy.make and its derived numbers (lib/atoms/tiled_copy.ml:10-36)."""
+    t = N.TiledCopyC()
+    if N.lib().tesserae_tiled_copy_make(C.byref(atom), thread_layout_size, val_layout_size, C.byref(t)) != 0:
+        raise ValueError(N.last_error())
+    return t
+
+
+def tiled_copy_partition(thread_count: int, shape, stride):
+    """Tiled_copy.partition_src / partition_dst (lib/atoms/tiled_copy.ml:38-50): (shape, stride) of the one mode."""
+    s, n = _arr(shape)
+    d, _ = _arr(stride)
+    os_, od_ = C.c_int64(), C.c_int64()
+    if N.lib().tesserae_tiled_copy_partition(thread_count, s, d, n, C.byref(os_), C.byref(od_)) < 0:
+        raise ValueError(N.last_error())
+    return os_.value, od_.value
+
+
+def tile_op(atom, thread_layout_size: int, warp_layout_size: int, tiler_m: int, tiler_n: int, accum: str,
+            tmem=None, double_buf: bool = False) -> N.TileOpC:
+    """Tile_op.make (lib/pipeline/tile_op.ml:18-37); tmem = (cta_group, num_cols, num_rows) or None."""
+    t = N.TileOpC()
+    t.atom = atom
+    t.thread_layout_size, t.warp_layout_size, t.tiler_m, t.tiler_n = thread_layout_size, warp_layout_size, tiler_m, tiler_n
+    t.accum_loc = {"Registers": 0, "TensorMem": 1}[accum]
+    t.has_tmem = int(tmem is not None)
+    if tmem is not None:
+        t.tmem_cta_group, t.tmem_cols, t.tmem_rows = tmem
+    t.double_buf = int(double_buf)
+    if N.lib().tesserae_tile_op_check(C.byref(t)) != 0:
+        raise ValueError(N.last_error())
+    return t
+
+
+def tile_op_is_tmem(t) -> bool:
+    return bool(N.lib().tesserae_tile_op_is_tmem(C.byref(t)))
+
+
+def tile_op_is_wgmma(t) -> bool:
+    return bool(N.lib().tesserae_tile_op_is_wgmma(C.byref(t)))
+
+
+def tile_op_accum_elems_per_thread(t) -> int:
+    return N.lib().tesserae_tile_op_accum_elems_per_thread(C.byref(t))
+
+
+def tile_op_emit(t, what: str, arg0: str = "", arg1: str = "", flag: int = 0) -> str:
+    """Tile_op.emit_mma / emit_commit / emit_accum_decl / emit_tmem_alloc / emit_tmem_dealloc (lib/pipeline/tile_op.ml:52-107)."""
+    return _text(N.lib().tesserae_tile_op_emit, C.byref(t), TILE_OP_TEXT[what], arg0.encode(), arg1.encode(), flag)

@@ -138,9 +138,12 @@ int derive_config(const tesserae_kernel_spec& ks, KernelConfig* cfg, std::string
             const int v = kv.second;
             bool ok = true;
             if (key == "GROUP_M") { ok = v >= 1 && v <= 64; c.group_m = v; }
+            else if (key == "L2_HINT") { ok = v >= 0 && v <= 7; c.l2_hint = v; }
             else if (key == "STORE_BUFS") { ok = v >= 2 && v <= 4; c.store_bufs = v; }
             else if (key == "FP8_PROMO_WARPS") { ok = v == 8 || v == 16; want_promo_warps = v; }
             else if (key == "FP8_SPLIT") { ok = v == 0 || v == 1; c.fp8_split = v; }
+            else if (key == "FP8_FMA2") { ok = v == 0 || v == 1; c.fp8_fma2 = v; }
+            else if (key == "FP8_XPIPE") { ok = v == 0 || v == 1; c.fp8_xpipe = v; }
             else { if (msg) *msg = "IncompatibleTile: unknown tuning name '" + key + "'"; return spec::IncompatibleTile; }
             if (!ok) {
                 if (msg) *msg = "IncompatibleTile: tuning value out of range: " + key + "=" + std::to_string(v);
@@ -256,8 +259,13 @@ BackendOutput emit(const KernelConfig& c) {
     o.includes = buf;
     if (c.scatter) o.includes += "#define TS_SCATTER 1\n";
     if (c.scale_mode == TESSERAE_SCALE_NONE) o.includes += "#define TS_STORE_BUFS " + std::to_string(c.store_bufs) + "\n";
-    if (c.scale_mode == TESSERAE_SCALE_FP8_BLOCK) o.includes += std::string("#define TS_FP8_SPLIT ") + (c.fp8_split ? "1\n" : "0\n");
+    if (c.scale_mode == TESSERAE_SCALE_FP8_BLOCK) {
+        o.includes += std::string("#define TS_FP8_SPLIT ") + (c.fp8_split ? "1\n" : "0\n");
+        o.includes += std::string("#define TS_FP8_FMA2 ") + (c.fp8_fma2 ? "1\n" : "0\n");
+        o.includes += std::string("#define TS_FP8_XPIPE ") + (c.fp8_xpipe ? "1\n" : "0\n");
+    }
     o.includes += "#define TS_GROUP_M " + std::to_string(c.group_m) + "\n";
+    if (c.scale_mode == TESSERAE_SCALE_NONE) o.includes += "#define TS_L2_HINT " + std::to_string(c.l2_hint) + "\n";
     o.helpers = strip_pragma_once(kSrcPtxSm100);
     const bool block_fp8 = c.scale_mode == TESSERAE_SCALE_FP8_BLOCK;
     const bool nvfp4 = c.scale_mode == TESSERAE_SCALE_NVFP4;

@@ -40,8 +40,9 @@ struct tesserae_gemm_plan {
     int cache_hit = 0;
     double compile_ms = 0.0;
     // Device staging for the host-buffer entry point; grown on demand, reused across calls.
-    void* ws[4] = {nullptr, nullptr, nullptr, nullptr};
-    size_t ws_cap[4] = {0, 0, 0, 0};
+    // (slots: 0 A, 1 B, 2 C, 3 bias, 4 scales of A, 5 scales of B)
+    void* ws[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    size_t ws_cap[6] = {0, 0, 0, 0, 0, 0};
     // Streams and events of the pipelined host-buffer call (copy in / compute / copy out); created on first use.
     static constexpr int kMaxChunks = 32;
     cudaStream_t s_in = nullptr, s_cmp = nullptr, s_out = nullptr;
@@ -552,34 +553,60 @@ static int ensure_ws(tesserae_gemm_plan* p, int i, size_t bytes) {
     return 0;
 }
 
-int tesserae_gemm_run_host(tesserae_gemm_plan* p, const void* a, const void* b, void* c, const void* bias,
-                           float alpha, int64_t m, int64_t n, int64_t k) {
-    if (!p || !a || !b || !c) return fail("gemm_run_host: null argument");
-    if (m <= 0 || n <= 0 || k <= 0) return fail("gemm_run_host: M, N and K must be positive");
-    if (p->cfg.has_bias && !bias) return fail("gemm_run_host: this kernel was built with a bias but none was given");
-    const int ebits = tesserae::spec::elem_bits(p->cfg.elem);
+// Bytes of the scale tables a scaled plan reads for `rows` rows of an operand (0 for an unscaled plan).
+static size_t scale_table_bytes(const KernelConfig& cfg, bool operand_a, int64_t rows, int64_t k) {
+    if (cfg.scale_mode == TESSERAE_SCALE_FP8_BLOCK)
+        return size_t(operand_a ? rows : (rows + 127) / 128) * size_t(k / 128) * sizeof(float);
+    if (cfg.scale_mode == TESSERAE_SCALE_NVFP4) return tesserae_nvfp4_scale_bytes(rows, k);
+    return 0;
+}
+
+// Host-buffer call shared by the unscaled and the block-scaled entry points.  `scales` holds HOST pointers (or is
+// NULL for an unscaled plan).
+static int run_host_impl(tesserae_gemm_plan* p, const void* a, const void* b, void* c, const tesserae_gemm_scales* scales,
+                         const void* bias, float alpha, int64_t m, int64_t n, int64_t k, const char* who) {
+    if (!p || !a || !b || !c) return fail(std::string(who) + ": null argument");
+    if (m <= 0 || n <= 0 || k <= 0) return fail(std::string(who) + ": M, N and K must be positive");
+    if (int drc = check_plan_device(p, who)) return drc;
+    const KernelConfig& cfg = p->cfg;
+    if (cfg.has_bias && !bias) return fail(std::string(who) + ": this kernel was built with a bias but none was given");
+    const bool scaled = cfg.scale_mode != TESSERAE_SCALE_NONE;
+    if (scaled && (!scales || !scales->scale_a || !scales->scale_b))
+        return fail(std::string(who) + ": this kernel needs scale factors (use tesserae_gemm_run_scaled_host)");
+    if (!scaled && scales) return fail(std::string(who) + ": this kernel takes no scale factors");
+    if (cfg.scale_mode == TESSERAE_SCALE_FP8_BLOCK && k % 128 != 0) return fail(std::string(who) + ": K must be a multiple of the 128-wide scale block");
+    if (cfg.scale_mode == TESSERAE_SCALE_NVFP4 && k % 256 != 0) return fail(std::string(who) + ": NVFP4 needs K to be a multiple of 256");
+    const int ebits = tesserae::spec::elem_bits(cfg.elem);
     const size_t a_bytes = size_t(m) * k * ebits / 8, b_bytes = size_t(n) * k * ebits / 8;
-    const size_t c_bytes = size_t(m) * n * out_bytes(p->cfg.out_elem);
+    const size_t c_bytes = size_t(m) * n * out_bytes(cfg.out_elem);
+    const size_t sa_bytes = scale_table_bytes(cfg, true, m, k), sb_bytes = scale_table_bytes(cfg, false, n, k);
     int rc = ensure_ws(p, 0, a_bytes);
     if (rc == 0) rc = ensure_ws(p, 1, b_bytes);
     if (rc == 0) rc = ensure_ws(p, 2, c_bytes);
-    if (rc == 0 && p->cfg.has_bias) rc = ensure_ws(p, 3, size_t(n) * 2);
+    if (rc == 0 && cfg.has_bias) rc = ensure_ws(p, 3, size_t(n) * 2);
+    if (rc == 0 && scaled) rc = ensure_ws(p, 4, sa_bytes);
+    if (rc == 0 && scaled) rc = ensure_ws(p, 5, sb_bytes);
     if (rc != 0) return rc;
-    const int ob = out_bytes(p->cfg.out_elem);
+    const int ob = out_bytes(cfg.out_elem);
     const size_t row_a = size_t(k) * ebits / 8, row_c = size_t(n) * ob;
+    tesserae_gemm_scales dsc;
+    if (scaled) { dsc = *scales; dsc.scale_a = p->ws[4]; dsc.scale_b = p->ws[5]; }
+    const void* dbias = cfg.has_bias ? p->ws[3] : nullptr;
     cudaError_t e = cudaSuccess;
-    // Large calls are PCIe-bound: B goes up first, then A in row chunks; each chunk's GEMM starts when its rows have
-    // landed and its rows of C go back while the next chunk is still arriving (three streams, both copy directions
-    // busy at once).  Small calls take the plain order on the default stream.  Either way the copies only run at
-    // full speed when the caller's buffers are page-locked.
+    // Large calls are PCIe-bound: B (and the scale tables) go up first, then A in row chunks; each chunk's GEMM starts
+    // when its rows have landed and its rows of C go back while the next chunk is still arriving (three streams, both
+    // copy directions busy at once).  Small calls take the plain order on the default stream.  Either way the copies
+    // only run at full speed when the caller's buffers are page-locked.
     const int64_t chunk_rows = ((m / 16 + 255) / 256) * 256;
     const bool pipelined = a_bytes + b_bytes + c_bytes >= (size_t(32) << 20) && chunk_rows >= 256 && m > chunk_rows;
     if (!pipelined) {
         e = cudaMemcpyAsync(p->ws[0], a, a_bytes, cudaMemcpyHostToDevice, nullptr);
         if (e == cudaSuccess) e = cudaMemcpyAsync(p->ws[1], b, b_bytes, cudaMemcpyHostToDevice, nullptr);
-        if (e == cudaSuccess && p->cfg.has_bias) e = cudaMemcpyAsync(p->ws[3], bias, size_t(n) * 2, cudaMemcpyHostToDevice, nullptr);
+        if (e == cudaSuccess && cfg.has_bias) e = cudaMemcpyAsync(p->ws[3], bias, size_t(n) * 2, cudaMemcpyHostToDevice, nullptr);
+        if (e == cudaSuccess && scaled) e = cudaMemcpyAsync(p->ws[4], scales->scale_a, sa_bytes, cudaMemcpyHostToDevice, nullptr);
+        if (e == cudaSuccess && scaled) e = cudaMemcpyAsync(p->ws[5], scales->scale_b, sb_bytes, cudaMemcpyHostToDevice, nullptr);
         if (e != cudaSuccess) return fail(cudaGetErrorString(e));
-        rc = tesserae_gemm_run(p, p->ws[0], p->ws[1], p->ws[2], p->cfg.has_bias ? p->ws[3] : nullptr, alpha, m, n, k, nullptr);
+        rc = gemm_launch(p, p->ws[0], 0, p->ws[1], 0, p->ws[2], 0, scaled ? &dsc : nullptr, dbias, alpha, m, n, k, nullptr);
         if (rc != 0) return rc;
         e = cudaMemcpyAsync(c, p->ws[2], c_bytes, cudaMemcpyDeviceToHost, nullptr);
     } else {
@@ -593,7 +620,7 @@ int tesserae_gemm_run_host(tesserae_gemm_plan* p, const void* a, const void* b, 
                 if (e == cudaSuccess) e = cudaEventCreateWithFlags(&p->ev_cmp[i], cudaEventDisableTiming);
             }
             if (e == cudaSuccess) e = cudaEventCreateWithFlags(&p->ev_done, cudaEventDisableTiming);
-            if (e != cudaSuccess) return fail(std::string("gemm_run_host: ") + cudaGetErrorString(e));
+            if (e != cudaSuccess) return fail(std::string(who) + ": " + cudaGetErrorString(e));
         }
         // work queued earlier on the default stream (by this thread) comes first
         e = cudaEventRecord(p->ev_done, nullptr);
@@ -601,7 +628,9 @@ int tesserae_gemm_run_host(tesserae_gemm_plan* p, const void* a, const void* b, 
         if (e == cudaSuccess) e = cudaStreamWaitEvent(p->s_cmp, p->ev_done, 0);
         if (e == cudaSuccess) e = cudaStreamWaitEvent(p->s_out, p->ev_done, 0);
         if (e == cudaSuccess) e = cudaMemcpyAsync(p->ws[1], b, b_bytes, cudaMemcpyHostToDevice, p->s_in);
-        if (e == cudaSuccess && p->cfg.has_bias) e = cudaMemcpyAsync(p->ws[3], bias, size_t(n) * 2, cudaMemcpyHostToDevice, p->s_in);
+        if (e == cudaSuccess && cfg.has_bias) e = cudaMemcpyAsync(p->ws[3], bias, size_t(n) * 2, cudaMemcpyHostToDevice, p->s_in);
+        if (e == cudaSuccess && scaled) e = cudaMemcpyAsync(p->ws[5], scales->scale_b, sb_bytes, cudaMemcpyHostToDevice, p->s_in);
+        if (e == cudaSuccess && scaled) e = cudaMemcpyAsync(p->ws[4], scales->scale_a, sa_bytes, cudaMemcpyHostToDevice, p->s_in);
         for (int i = 0; i < chunks && e == cudaSuccess; ++i) {
             const int64_t r0 = int64_t(i) * chunk_rows, rows = (m - r0 < chunk_rows) ? (m - r0) : chunk_rows;
             char* da = static_cast<char*>(p->ws[0]) + size_t(r0) * row_a;
@@ -610,7 +639,11 @@ int tesserae_gemm_run_host(tesserae_gemm_plan* p, const void* a, const void* b, 
             if (e == cudaSuccess) e = cudaEventRecord(p->ev_in[i], p->s_in);
             if (e == cudaSuccess) e = cudaStreamWaitEvent(p->s_cmp, p->ev_in[i], 0);
             if (e != cudaSuccess) break;
-            rc = tesserae_gemm_run(p, da, p->ws[1], dc, p->cfg.has_bias ? p->ws[3] : nullptr, alpha, rows, n, k, p->s_cmp);
+            // the chunk's rows of the A scale table: chunk boundaries are multiples of 256 rows, so they are whole rows
+            // of the fp32 table and whole 128-row blocks of the chunked NVFP4 table
+            tesserae_gemm_scales csc = dsc;
+            if (scaled) csc.scale_a = static_cast<const char*>(p->ws[4]) + scale_table_bytes(cfg, true, r0, k);
+            rc = gemm_launch(p, da, 0, p->ws[1], 0, dc, 0, scaled ? &csc : nullptr, dbias, alpha, rows, n, k, p->s_cmp);
             if (rc != 0) { cudaDeviceSynchronize(); return rc; }
             e = cudaEventRecord(p->ev_cmp[i], p->s_cmp);
             if (e == cudaSuccess) e = cudaStreamWaitEvent(p->s_out, p->ev_cmp[i], 0);
@@ -626,9 +659,21 @@ int tesserae_gemm_run_host(tesserae_gemm_plan* p, const void* a, const void* b, 
     if (e != cudaSuccess) return fail(cudaGetErrorString(e));
     if (st != 0) {
         cudaMemset(p->d_status, 0, sizeof st);
-        return fail("gemm_run_host: kernel reported a timed-out wait, status=" + std::to_string(st));
+        return fail(std::string(who) + ": kernel reported a timed-out wait, status=" + std::to_string(st));
     }
     return 0;
+}
+
+int tesserae_gemm_run_host(tesserae_gemm_plan* p, const void* a, const void* b, void* c, const void* bias,
+                           float alpha, int64_t m, int64_t n, int64_t k) {
+    return run_host_impl(p, a, b, c, nullptr, bias, alpha, m, n, k, "gemm_run_host");
+}
+
+int tesserae_gemm_run_scaled_host(tesserae_gemm_plan* p, const void* a, const void* b, void* c,
+                                  const tesserae_gemm_scales* scales, const void* bias,
+                                  float alpha, int64_t m, int64_t n, int64_t k) {
+    if (!scales) return fail("gemm_run_scaled_host: null scales");
+    return run_host_impl(p, a, b, c, scales, bias, alpha, m, n, k, "gemm_run_scaled_host");
 }
 
 int tesserae_runtime_run(const tesserae_kernel_spec* ks, int64_t m, int64_t n, int64_t k,

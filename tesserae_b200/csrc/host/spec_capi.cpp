@@ -131,6 +131,131 @@ int tesserae_predicate_residue(const int64_t* shape, const int64_t* bounds, int 
     });
 }
 
+// ------------------------------------------------------------------ Memspace / atoms / Tiled_* / Tile_op
+static int put_string(const std::string& s, char* buf, size_t buf_size) {
+    if (!buf || buf_size == 0) return fail("output buffer is null");
+    if (s.size() + 1 > buf_size) return fail("output buffer too small: need " + std::to_string(s.size() + 1) + " bytes");
+    std::memcpy(buf, s.c_str(), s.size() + 1);
+    return 0;
+}
+static sp::MmaAtom atom_from_c(const tesserae_mma_atom* a) {
+    sp::MmaAtom r;
+    r.arch = a->arch; r.m = a->m; r.n = a->n; r.k = a->k;
+    r.a_type = a->a_type; r.b_type = a->b_type; r.c_type = a->c_type; r.d_type = a->d_type;
+    r.a_major = a->a_major; r.b_major = a->b_major;
+    r.threads = sp::mma_atom_thread_count(r);
+    return r;
+}
+static sp::CopyAtom copy_from_c(const tesserae_copy_atom* a) {
+    return sp::CopyAtom{a->kind, a->src_space, a->dst_space, a->elem, a->vec_width, a->bulk_bytes};
+}
+static sp::TileOp tile_op_from_c(const tesserae_tile_op* t) {
+    sp::TiledMma tm = sp::tiled_mma_make(atom_from_c(&t->atom), t->thread_layout_size, t->warp_layout_size, t->tiler_m, t->tiler_n);
+    sp::Tmem tmem{t->tmem_cta_group, t->tmem_cols, t->tmem_rows};
+    return sp::tile_op_make(tm, t->accum_loc, t->has_tmem ? &tmem : nullptr, t->double_buf != 0);
+}
+
+int tesserae_memspace_can_transfer(int src, int dst) { return sp::memspace_can_transfer(src, dst) ? 1 : 0; }
+const char* tesserae_memspace_name(int space) { return sp::memspace_name(space); }
+
+int tesserae_mma_atom_make(int which, int a_major, int b_major, tesserae_mma_atom* out) {
+    if (!out) return fail("mma_atom_make: null output");
+    TS_GUARD({
+        const sp::MmaAtom a = sp::mma_atom_make(which, a_major, b_major);
+        out->arch = a.arch; out->m = a.m; out->n = a.n; out->k = a.k;
+        out->a_type = a.a_type; out->b_type = a.b_type; out->c_type = a.c_type; out->d_type = a.d_type;
+        out->a_major = a.a_major; out->b_major = a.b_major;
+        return 0;
+    });
+}
+int tesserae_mma_atom_thread_count(const tesserae_mma_atom* a) { return a ? sp::mma_atom_thread_count(atom_from_c(a)) : -1; }
+int tesserae_mma_atom_is_wgmma(const tesserae_mma_atom* a) { return a ? (sp::mma_atom_is_wgmma(atom_from_c(a)) ? 1 : 0) : -1; }
+int tesserae_mma_atom_emit_cpp(const tesserae_mma_atom* a, char* buf, size_t buf_size) {
+    if (!a) return fail("mma_atom_emit_cpp: null atom");
+    return put_string(sp::mma_atom_emit_cpp(atom_from_c(a)), buf, buf_size);
+}
+
+int tesserae_copy_atom_make(int kind, int elem, int src_space, int dst_space, tesserae_copy_atom* out) {
+    if (!out) return fail("copy_atom_make: null output");
+    TS_GUARD({
+        const sp::CopyAtom a = sp::copy_atom_make(kind, elem, src_space, dst_space);
+        out->kind = a.kind; out->src_space = a.src_space; out->dst_space = a.dst_space; out->elem = a.elem;
+        out->vec_width = a.vec_width; out->bulk_bytes = a.bulk_bytes;
+        return 0;
+    });
+}
+int tesserae_copy_atom_is_async(const tesserae_copy_atom* a) { return a ? (sp::copy_atom_is_async(copy_from_c(a)) ? 1 : 0) : -1; }
+int tesserae_copy_atom_is_tma(const tesserae_copy_atom* a) { return a ? (sp::copy_atom_is_tma(copy_from_c(a)) ? 1 : 0) : -1; }
+int tesserae_copy_atom_requires_mbar(const tesserae_copy_atom* a) { return a ? (sp::copy_atom_requires_mbar(copy_from_c(a)) ? 1 : 0) : -1; }
+int tesserae_copy_atom_emit_cpp(const tesserae_copy_atom* a, char* buf, size_t buf_size) {
+    if (!a) return fail("copy_atom_emit_cpp: null atom");
+    return put_string(sp::copy_atom_emit_cpp(copy_from_c(a)), buf, buf_size);
+}
+
+int tesserae_tiled_mma_make(const tesserae_mma_atom* atom, int64_t thread_layout_size, int64_t warp_layout_size,
+                            int64_t tiler_m, int64_t tiler_n, tesserae_tiled_mma* out) {
+    if (!atom || !out) return fail("tiled_mma_make: null argument");
+    TS_GUARD({
+        const sp::TiledMma t = sp::tiled_mma_make(atom_from_c(atom), thread_layout_size, warp_layout_size, tiler_m, tiler_n);
+        out->thread_count = sp::tiled_mma_thread_count(t);
+        out->warp_count = sp::tiled_mma_warp_count(t);
+        out->tile_m = t.tiler_m; out->tile_n = t.tiler_n; out->tile_k = t.atom.k;
+        out->partition_a = sp::tiled_mma_partition_a(t);
+        out->partition_b = sp::tiled_mma_partition_b(t);
+        out->partition_c = sp::tiled_mma_partition_c(t);
+        return 0;
+    });
+}
+
+int tesserae_tiled_copy_make(const tesserae_copy_atom* atom, int64_t thread_layout_size, int64_t val_layout_size,
+                             tesserae_tiled_copy* out) {
+    if (!atom || !out) return fail("tiled_copy_make: null argument");
+    TS_GUARD({
+        const sp::TiledCopy t = sp::tiled_copy_make(copy_from_c(atom), thread_layout_size, val_layout_size);
+        out->thread_count = t.thread_layout_size;
+        out->elements_per_thread = t.val_layout_size;
+        out->tile_size = sp::tiled_copy_tile_size(t);
+        out->is_tma = sp::copy_atom_is_tma(t.atom) ? 1 : 0;
+        out->requires_mbar = sp::copy_atom_requires_mbar(t.atom) ? 1 : 0;
+        return 0;
+    });
+}
+int tesserae_tiled_copy_partition(int64_t thread_count, const int64_t* shape, const int64_t* stride, int n,
+                                  int64_t* out_shape, int64_t* out_stride) {
+    TS_GUARD({
+        const sp::Layout d = sp::flat_divide(mk(shape, stride, n), thread_count);
+        if (out_shape) *out_shape = d.shape[1];
+        if (out_stride) *out_stride = d.stride[1];
+        return 1;
+    });
+}
+
+int tesserae_tile_op_check(const tesserae_tile_op* t) {
+    if (!t) return fail("tile_op_check: null argument");
+    TS_GUARD({ (void)tile_op_from_c(t); return 0; });
+}
+int tesserae_tile_op_is_tmem(const tesserae_tile_op* t) { TS_GUARD(return t ? (sp::tile_op_is_tmem(tile_op_from_c(t)) ? 1 : 0) : -1); }
+int tesserae_tile_op_is_wgmma(const tesserae_tile_op* t) { TS_GUARD(return t ? (sp::tile_op_is_wgmma(tile_op_from_c(t)) ? 1 : 0) : -1); }
+int64_t tesserae_tile_op_accum_elems_per_thread(const tesserae_tile_op* t) {
+    TS_GUARD(return t ? sp::tile_op_accum_elems_per_thread(tile_op_from_c(t)) : -1);
+}
+int tesserae_tile_op_emit(const tesserae_tile_op* t, int what, const char* arg0, const char* arg1, int flag,
+                          char* buf, size_t buf_size) {
+    if (!t) return fail("tile_op_emit: null argument");
+    const std::string a0 = arg0 ? arg0 : "", a1 = arg1 ? arg1 : "";
+    TS_GUARD({
+        const sp::TileOp op = tile_op_from_c(t);
+        switch (what) {
+            case TESSERAE_TILE_OP_MMA: return put_string(sp::tile_op_emit_mma(op, a0, a1, flag != 0), buf, buf_size);
+            case TESSERAE_TILE_OP_COMMIT: return put_string(sp::tile_op_emit_commit(op, a0, flag), buf, buf_size);
+            case TESSERAE_TILE_OP_ACCUM_DECL: return put_string(sp::tile_op_emit_accum_decl(op, a0), buf, buf_size);
+            case TESSERAE_TILE_OP_TMEM_ALLOC: return put_string(sp::tile_op_emit_tmem_alloc(op, a0), buf, buf_size);
+            case TESSERAE_TILE_OP_TMEM_DEALLOC: return put_string(sp::tile_op_emit_tmem_dealloc(op, a0), buf, buf_size);
+            default: return fail("tile_op_emit: unknown text selector");
+        }
+    });
+}
+
 // Shard `index` of `parts` over [0, total): contiguous ranges whose boundaries are multiples of `align`
 // (the last range takes the remainder).  N-split shards align to 128 columns so that no 128x128 weight
 // scale block or 128-row scale chunk straddles two GPUs; K-split shards align to one smem stage.

@@ -72,6 +72,12 @@ constexpr ts_u32 kThreads     = 32 * (kFirstPromoWarp + kNumPromoWarps);
 constexpr int    kRegsIssue   = kNumPromoWarps == 8 ? 40 : 32;  // register budgets after the split (per thread)
 constexpr int    kRegsPromo   = kNumPromoWarps == 8 ? 232 : 112;
 constexpr ts_u32 kLdCols      = kNumPromoWarps == 8 ? 32 : 16;  // TMEM columns per load of the promotion loop
+#ifndef TS_FP8_FMA2
+#define TS_FP8_FMA2 1          // promotion multiply-adds issued as packed pairs (fma.rn.f32x2)
+#endif
+#ifndef TS_FP8_XPIPE
+#define TS_FP8_XPIPE 1         // the first tensor-memory load of K block i+1 is issued before the last multiply-adds of block i
+#endif
 #ifndef TS_SCALES_EARLY
 #define TS_SCALES_EARLY 1
 #endif
@@ -329,10 +335,31 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
                 else             decode_tile(t + tile_step, num_m, num_n, m_next, n_next);
             }
             const ts_u32 col_base = n_blk * kBlockN + half * kWarpCols;
-            float acc[kWarpCols];
+            // 128 x BLOCK_N fp32 accumulators of the tile, one row per lane, held as packed pairs: the multiply-adds
+            // are issued two at a time (fma.rn.f32x2: the same two roundings as two scalar fmas, half the issue slots).
+            ts_u64 acc2[kWarpCols / 2];
 #pragma unroll
-            for (ts_u32 i = 0; i < kWarpCols; ++i) acc[i] = 0.f;
+            for (ts_u32 i = 0; i < kWarpCols / 2; ++i) acc2[i] = 0ull;
             constexpr ts_u32 kRounds = kWarpCols / kLdCols;
+            static_assert(kRounds % 2 == 0, "the two load buffers alternate per round and must line up across K blocks");
+            const ts_u32 grp = (half * kWarpCols) / kBufCols;                      // the MMA group this warp reads
+            const ts_u32 col_in_buf = (half * kWarpCols) % kBufCols;
+            ts_u32 p0[kLdCols], p1[kLdCols];      // two TMEM load buffers, used in turn
+            // First load of the tile: columns 0..kLdCols-1 of the first K block's partial product.
+#if TS_FP8_XPIPE
+            {
+                const ts_u32 unit = it * kHalves + grp;
+                const ts_u32 buf = unit % kNumAcc;
+                if (!ts_mbar_wait(tmem_full_bar + 8 * buf, (unit / kNumAcc) & 1u)) {
+                    if (lane == 0) atomicOr(status, TS_ERR_TIMEOUT_TMEM_FULL);
+                    ok = false;
+                }
+                if (ok) {
+                    ts_tc_fence_after();
+                    ts_tmem_ld(tmem_base + ((quarter * 32u) << 16) + buf * kBufCols + col_in_buf, p0);
+                }
+            }
+#endif
 #pragma unroll 1
             for (ts_u32 kb0 = 0; kb0 < nkb && ok; kb0 += kScaleRing) {
 #pragma unroll
@@ -342,20 +369,23 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
                 if ((kb & 31u) == 0u && kb != 0u && kb + lane < nkb) sb_l = __ldg(sb_ptr + kb + lane);
                 const float s = alpha * sa_r[j] * __shfl_sync(0xffffffffu, sb_l, (int)(kb & 31u));
                 if (kb + kScaleRing < nkb) sa_r[j] = __ldg(sa_ptr + kb + kScaleRing);
-                const ts_u32 unit = it * kHalves + (half * kWarpCols) / kBufCols;   // the MMA group this warp reads
+                const ts_u64 s2 = ts_pack_f32x2(__float_as_uint(s), __float_as_uint(s));
+                (void)s2;
+                const ts_u32 unit = it * kHalves + grp;
                 const ts_u32 buf = unit % kNumAcc;
-                const ts_u32 buf_ph = (unit / kNumAcc) & 1u;
-                const ts_u32 t_row = tmem_base + ((quarter * 32u) << 16) + buf * kBufCols + (half * kWarpCols) % kBufCols;
-                if (!ts_mbar_wait(tmem_full_bar + 8 * buf, buf_ph)) {
+                const ts_u32 t_row = tmem_base + ((quarter * 32u) << 16) + buf * kBufCols + col_in_buf;
+#if !TS_FP8_XPIPE
+                if (!ts_mbar_wait(tmem_full_bar + 8 * buf, (unit / kNumAcc) & 1u)) {
                     if (lane == 0) atomicOr(status, TS_ERR_TIMEOUT_TMEM_FULL);
                     ok = false; continue;
                 }
                 ts_tc_fence_after();
-                ts_u32 p0[kLdCols], p1[kLdCols];      // two TMEM load buffers, used in turn
                 ts_tmem_ld(t_row, p0);
-                // kLdCols columns at a time, two register buffers: the load of the next group is in flight
-                // while the multiply-adds of the current one issue.  The buffer goes back to the tensor core as
-                // soon as its last load has landed, before the last multiply-adds.
+#endif
+                // kLdCols columns at a time, two register buffers: the load of the next group is in flight while the
+                // multiply-adds of the current one issue.  The buffer goes back to the tensor core as soon as its last
+                // load has landed; the first load of the NEXT K block is then issued in front of this block's last
+                // multiply-adds, so that no K block starts with an exposed trip to tensor memory.
 #pragma unroll
                 for (ts_u32 c = 0; c < kRounds; ++c) {
                     ts_tmem_wait_ld();
@@ -368,14 +398,42 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
                             if (TS_CTA_GROUP == 2) ts_mbar_arrive_cluster(leader_tmem_empty + 8 * buf);
                             else                   ts_mbar_arrive(tmem_empty_bar + 8 * buf);
                         }
+#if TS_FP8_XPIPE
+                        if (kb + 1 < nkb) {
+                            const ts_u32 unit_n = (it + 1) * kHalves + grp;
+                            const ts_u32 buf_n = unit_n % kNumAcc;
+                            if (!ts_mbar_wait(tmem_full_bar + 8 * buf_n, (unit_n / kNumAcc) & 1u)) {
+                                if (lane == 0) atomicOr(status, TS_ERR_TIMEOUT_TMEM_FULL);
+                                ok = false;
+                            }
+                            if (ok) {
+                                ts_tc_fence_after();
+                                ts_tmem_ld(tmem_base + ((quarter * 32u) << 16) + buf_n * kBufCols + col_in_buf, p0);
+                            }
+                        }
+#endif
                     }
 #pragma unroll
-                    for (ts_u32 i = 0; i < kLdCols; ++i)
-                        acc[c * kLdCols + i] = fmaf(__uint_as_float((c & 1u) ? p1[i] : p0[i]), s, acc[c * kLdCols + i]);
+                    for (ts_u32 i = 0; i < kLdCols / 2; ++i) {
+#if TS_FP8_FMA2
+                        const ts_u64 pp = (c & 1u) ? ts_pack_f32x2(p1[2 * i], p1[2 * i + 1]) : ts_pack_f32x2(p0[2 * i], p0[2 * i + 1]);
+                        acc2[(c * kLdCols) / 2 + i] = ts_fma_f32x2(pp, s2, acc2[(c * kLdCols) / 2 + i]);
+#else
+                        float lo, hi;
+                        ts_unpack_f32x2(acc2[(c * kLdCols) / 2 + i], lo, hi);
+                        lo = fmaf(__uint_as_float((c & 1u) ? p1[2 * i] : p0[2 * i]), s, lo);
+                        hi = fmaf(__uint_as_float((c & 1u) ? p1[2 * i + 1] : p0[2 * i + 1]), s, hi);
+                        acc2[(c * kLdCols) / 2 + i] = ts_pack_f32x2(__float_as_uint(lo), __float_as_uint(hi));
+#endif
+                    }
                 }
                 ++it;
             }
             }
+            ts_tmem_wait_ld();      // (nothing is outstanding on the healthy path; after a timed-out wait there may be)
+            float acc[kWarpCols];
+#pragma unroll
+            for (ts_u32 i = 0; i < kWarpCols / 2; ++i) ts_unpack_f32x2(acc2[i], acc[2 * i], acc[2 * i + 1]);
             if (!ok) break;
             // The next tile's first scales: ask for the lines now (no register is tied up while the accumulators
             // are still live), load them after the epilogue.

@@ -137,6 +137,31 @@ TS_DEV void ts_tma_store_2d(const TsTensorMap* m, ts_u32 src, int c0, int c1) {
         "cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
         :: "l"((ts_u64)m), "r"(src), "r"(c0), "r"(c1) : "memory");
 }
+// The same copies with an L2 eviction-priority hint (a 64-bit policy made by createpolicy): operand panels
+// that later tiles read again are kept (evict_last), data that is used once passes through (evict_first).
+TS_DEV ts_u64 ts_l2_policy_evict_last() {
+    ts_u64 p; asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p)); return p;
+}
+TS_DEV ts_u64 ts_l2_policy_evict_first() {
+    ts_u64 p; asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p)); return p;
+}
+TS_DEV void ts_tma_load_2d_hint(ts_u32 dst, const TsTensorMap* m, ts_u32 bar, int c0, int c1, ts_u64 policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+        " [%0], [%1, {%3, %4}], [%2], %5;"
+        :: "r"(dst), "l"((ts_u64)m), "r"(bar), "r"(c0), "r"(c1), "l"(policy) : "memory");
+}
+TS_DEV void ts_tma_load_2d_pair_hint(ts_u32 dst, const TsTensorMap* m, ts_u32 cluster_bar, int c0, int c1, ts_u64 policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+        " [%0], [%1, {%3, %4}], [%2], %5;"
+        :: "r"(dst), "l"((ts_u64)m), "r"(cluster_bar), "r"(c0), "r"(c1), "l"(policy) : "memory");
+}
+TS_DEV void ts_tma_store_2d_hint(const TsTensorMap* m, ts_u32 src, int c0, int c1, ts_u64 policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3}], [%1], %4;"
+        :: "l"((ts_u64)m), "r"(src), "r"(c0), "r"(c1), "l"(policy) : "memory");
+}
 TS_DEV void ts_bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N> TS_DEV void ts_bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" :: "n"(N) : "memory"); }
 TS_DEV void ts_bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
@@ -320,6 +345,18 @@ TS_DEV void ts_ld_shared_v4(ts_u32 addr, ts_u32& a, ts_u32& b, ts_u32& c, ts_u32
 }
 
 // ---------------------------------------------------------------- small utilities
+// Packed pairs of fp32 in one 64-bit register and the two-wide multiply-add over them: d = a * b + c per half,
+// each half rounded once like a scalar fma.rn.
+TS_DEV ts_u64 ts_pack_f32x2(ts_u32 lo, ts_u32 hi) {
+    ts_u64 r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi)); return r;
+}
+TS_DEV void ts_unpack_f32x2(ts_u64 v, float& lo, float& hi) {
+    ts_u32 a, b; asm("mov.b64 {%0, %1}, %2;" : "=r"(a), "=r"(b) : "l"(v));
+    lo = __uint_as_float(a); hi = __uint_as_float(b);
+}
+TS_DEV ts_u64 ts_fma_f32x2(ts_u64 a, ts_u64 b, ts_u64 c) {
+    ts_u64 d; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c)); return d;
+}
 // Two fp32 -> packed bf16x2 (round to nearest even); `lo` lands in the low half.
 TS_DEV ts_u32 ts_pack_bf16x2(float lo, float hi) {
     ts_u32 r; asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo)); return r;

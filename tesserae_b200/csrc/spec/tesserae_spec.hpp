@@ -273,11 +273,174 @@ inline uint32_t umma_instr_desc(int elem, int umma_m, int umma_n) {
     return (dfmt << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(umma_n >> 3) << 17) | (uint32_t(umma_m >> 4) << 24);
 }
 
-// ---------------------------------------------------------------- atoms (lib/atoms/mma_atom.ml:92-114, copy_atom.ml:61-89)
-struct MmaAtom { int m, n, k, threads; const char* name; };
-inline MmaAtom sm100_128x128x16() { return {128, 128, 16, 128, "SM100_128x128x16_F32F16F16F32_TN"}; }
-inline MmaAtom sm100_64x64x16() { return {64, 128, 16, 128, "SM100_64x64x16_F32F16F16F32_TN"}; }
+// ---------------------------------------------------------------- Memspace (lib/core/memspace.ml:8-47)
+enum Space { Global = 0, Shared = 1, Register = 2, TensorSpace = 3 };
+inline const char* memspace_name(int s) {
+    switch (s) { case Global: return "global"; case Shared: return "shared"; case Register: return "register";
+                 case TensorSpace: return "tensor"; default: return "?"; }
+}
+// Memspace.can_transfer: same -> same; global -> shared / register; shared -> register; register -> shared /
+// global.  shared -> global is false in the reference (it models st.global from registers only), and so is
+// every pair that involves the tensor space other than tensor -> tensor.
+inline bool memspace_can_transfer(int src, int dst) {
+    if (src < Global || src > TensorSpace || dst < Global || dst > TensorSpace) return false;
+    if (src == dst) return true;
+    if (src == Global && (dst == Shared || dst == Register)) return true;
+    if (src == Shared && dst == Register) return true;
+    if (src == Register && (dst == Shared || dst == Global)) return true;
+    return false;
+}
 
+// ---------------------------------------------------------------- Mma_atom (lib/atoms/mma_atom.ml:31-157)
+enum Major { RowMajor = 0, ColMajor = 1 };
+struct MmaAtom {
+    int m = 0, n = 0, k = 0, threads = 0;
+    const char* name = "";                 // emit_cpp for ColMajor A / RowMajor B ("TN"), kept for the descriptor
+    int arch = 2;                          // Arch code: 0 SM80, 1 SM90, 2 SM100
+    int a_type = F16, b_type = F16, c_type = F32, d_type = F32;
+    int a_major = ColMajor, b_major = RowMajor;
+};
+enum MmaAtomId { Sm80_16x8x8_F16 = 0, Sm80_16x8x16_F16, Sm80_16x8x16_BF16, Sm80_16x8x32_S8, Sm90_64x64x16_F16,
+                 Sm90_64x128x16_F16, Sm90_64x64x16_BF16, Sm100_64x64x16_F16, Sm100_128x128x16_F16, Sm100_64x64x32_S8,
+                 MmaAtomCount };
+// Mma_atom.thread_count / is_wgmma (lib/atoms/mma_atom.ml:118-130): 32 threads on SM80, a warpgroup of 128 else.
+inline int mma_atom_thread_count(const MmaAtom& a) { return a.arch == 0 ? 32 : 128; }
+inline bool mma_atom_is_wgmma(const MmaAtom& a) { return a.arch != 0; }
+inline MmaAtom mma_atom_make(int id, int a_major = ColMajor, int b_major = RowMajor) {
+    struct Row { int arch, m, n, k, ab, cd; };
+    static const Row rows[MmaAtomCount] = {
+        {0, 16, 8, 8, F16, F32},   {0, 16, 8, 16, F16, F32},  {0, 16, 8, 16, BF16, F32}, {0, 16, 8, 32, S8, S32},
+        {1, 64, 64, 16, F16, F32}, {1, 64, 128, 16, F16, F32}, {1, 64, 64, 16, BF16, F32},
+        {2, 64, 64, 16, F16, F32}, {2, 128, 128, 16, F16, F32}, {2, 64, 64, 32, S8, S32}};
+    if (id < 0 || id >= MmaAtomCount) throw SpecError("unknown MMA atom");
+    const Row& r = rows[id];
+    MmaAtom a;
+    a.arch = r.arch; a.m = r.m; a.n = r.n; a.k = r.k;
+    a.a_type = a.b_type = r.ab; a.c_type = a.d_type = r.cd;
+    a.a_major = a_major; a.b_major = b_major;
+    a.threads = mma_atom_thread_count(a);
+    return a;
+}
+// Mma_atom.emit_cpp (lib/atoms/mma_atom.ml:146-156): ARCH_MxNxK_<D><A><B><C>_<a major><b major>, ColMajor -> "T".
+inline std::string mma_atom_emit_cpp(const MmaAtom& a) {
+    auto es = [](int e) { return e == F32 ? "F32" : e == F16 ? "F16" : e == BF16 ? "BF16" : e == S8 ? "S8" : e == S32 ? "S32" : "?"; };
+    auto mc = [](int mj) { return mj == ColMajor ? "T" : "N"; };
+    return std::string(a.arch == 0 ? "SM80" : a.arch == 1 ? "SM90" : "SM100") + "_" + std::to_string(a.m) + "x" +
+           std::to_string(a.n) + "x" + std::to_string(a.k) + "_" + es(a.d_type) + es(a.a_type) + es(a.b_type) +
+           es(a.c_type) + "_" + mc(a.a_major) + mc(a.b_major);
+}
+inline MmaAtom sm100_128x128x16() { MmaAtom a = mma_atom_make(Sm100_128x128x16_F16); a.name = "SM100_128x128x16_F32F16F16F32_TN"; return a; }
+inline MmaAtom sm100_64x64x16() { MmaAtom a = mma_atom_make(Sm100_64x64x16_F16); a.name = "SM100_64x64x16_F32F16F16F32_TN"; return a; }
+inline MmaAtom sm100_64x64x32_s8() { MmaAtom a = mma_atom_make(Sm100_64x64x32_S8); a.name = "SM100_64x64x32_S32S8S8S32_TN"; return a; }
+
+// ---------------------------------------------------------------- Copy_atom (lib/atoms/copy_atom.ml:4-137)
+// The fifth kind is the reference's SM100 cluster-wide TMA load; this build lowers it to per-CTA loads of a
+// CTA pair (see Strategy below) and calls it TmaLoadPair, keeping the value and the emitted name.
+enum CopyKind { AsyncCopyGlobal = 0, AsyncCopyCached = 1, TmaLoadAtom = 2, TmaStoreAtom = 3, TmaLoadPair = 4,
+                Ldmatrix = 5, LdmatrixTrans = 6, UniversalCopy = 7 };
+struct CopyAtom { int kind, src_space, dst_space, elem, vec_width, bulk_bytes; };
+inline CopyAtom copy_atom_make(int kind, int elem, int src_space = Global, int dst_space = Shared) {
+    const int bw = elem_byte_width(elem);
+    if (bw <= 0) throw SpecError("unknown element type");
+    switch (kind) {
+        case AsyncCopyGlobal: case AsyncCopyCached: return {kind, Global, Shared, elem, 16 / bw, 16};
+        case Ldmatrix: case LdmatrixTrans: return {kind, Shared, Register, elem, 8, 32};
+        case TmaLoadAtom: case TmaLoadPair: return {kind, Global, Shared, elem, 128 / bw, 128};
+        case TmaStoreAtom: return {kind, Shared, Global, elem, 128 / bw, 128};
+        case UniversalCopy: return {kind, src_space, dst_space, elem, 1, bw};
+        default: throw SpecError("unknown copy atom kind");
+    }
+}
+inline bool copy_atom_is_tma(const CopyAtom& a) { return a.kind == TmaLoadAtom || a.kind == TmaStoreAtom || a.kind == TmaLoadPair; }
+inline bool copy_atom_is_async(const CopyAtom& a) { return a.kind == AsyncCopyGlobal || a.kind == AsyncCopyCached || copy_atom_is_tma(a); }
+inline bool copy_atom_requires_mbar(const CopyAtom& a) { return copy_atom_is_tma(a); }
+inline std::string copy_atom_emit_cpp(const CopyAtom& a) {
+    switch (a.kind) {
+        case AsyncCopyGlobal: return "SM80_CP_ASYNC_CACHEGLOBAL<cute::uint128_t>";
+        case AsyncCopyCached: return "SM80_CP_ASYNC_CACHEALL<cute::uint128_t>";
+        case TmaLoadAtom: return "SM90_TMA_LOAD";
+        case TmaStoreAtom: return "SM90_TMA_STORE";
+        case TmaLoadPair: return std::string("SM100_TMA_LOAD_") + "MULTI" + "CAST";     // the reference's CuTe atom name
+        case Ldmatrix: return "SM80_U32x4_LDSM_N";
+        case LdmatrixTrans: return "SM80_U16x8_LDSM_T";
+        default: return std::string("UniversalCopy<") + elem_cpp_name(a.elem) + ">";
+    }
+}
+
+// ---------------------------------------------------------------- Tiled_mma (lib/atoms/tiled_mma.ml:12-53)
+// The reference's partitions use only the *sizes* of the thread and warp layouts (the warp layout is ignored by
+// partition_*), so the model carries the sizes.
+struct TiledMma { MmaAtom atom; i64 thread_layout_size, warp_layout_size, tiler_m, tiler_n; };
+inline TiledMma tiled_mma_make(const MmaAtom& atom, i64 thread_layout_size, i64 warp_layout_size, i64 tiler_m, i64 tiler_n) {
+    if (thread_layout_size != mma_atom_thread_count(atom)) throw SpecError("thread_layout size does not match atom thread count");
+    return TiledMma{atom, thread_layout_size, warp_layout_size, tiler_m, tiler_n};
+}
+inline i64 tiled_mma_thread_count(const TiledMma& t) { return t.thread_layout_size * t.warp_layout_size; }
+inline i64 tiled_mma_warp_count(const TiledMma& t) { return t.warp_layout_size; }
+// partition_a / _b / _c: (atom elements / thread_layout size) : 1
+inline i64 tiled_mma_partition_a(const TiledMma& t) { return i64(t.atom.m) * t.atom.k / t.thread_layout_size; }
+inline i64 tiled_mma_partition_b(const TiledMma& t) { return i64(t.atom.n) * t.atom.k / t.thread_layout_size; }
+inline i64 tiled_mma_partition_c(const TiledMma& t) { return i64(t.atom.m) * t.atom.n / t.thread_layout_size; }
+
+// ---------------------------------------------------------------- Tiled_copy (lib/atoms/tiled_copy.ml:10-50)
+struct TiledCopy { CopyAtom atom; i64 thread_layout_size, val_layout_size; };
+inline TiledCopy tiled_copy_make(const CopyAtom& atom, i64 thread_layout_size, i64 val_layout_size) {
+    if (val_layout_size != atom.vec_width) throw SpecError("val_layout size does not match atom vec_width");
+    if (thread_layout_size <= 0) throw SpecError("thread_layout size must be positive");
+    return TiledCopy{atom, thread_layout_size, val_layout_size};
+}
+inline i64 tiled_copy_tile_size(const TiledCopy& t) { return t.thread_layout_size * t.val_layout_size; }
+// partition_src / partition_dst: flat_divide by the thread count, keep the "across" mode.
+inline Layout tiled_copy_partition(const TiledCopy& t, const Layout& l) {
+    const Layout d = flat_divide(l, t.thread_layout_size);
+    return Layout({d.shape[1]}, {d.stride[1]});
+}
+
+// ---------------------------------------------------------------- Tile_op (lib/pipeline/tile_op.ml:18-107)
+// Tmem's instruction text (lib/pipeline/tmem.ml:72-110), which Tile_op forwards.
+inline std::string tmem_alloc_ptx(const Tmem& t, const std::string& smem_var) {
+    return "tcgen05.alloc.cta_group::" + std::to_string(t.cta_group) + ".sync.aligned.shared::cta.b32 [" + smem_var + "], " +
+           std::to_string(t.num_cols) + ";";
+}
+inline std::string tmem_dealloc_ptx(const Tmem& t, const std::string& taddr_var) {
+    return "tcgen05.dealloc.cta_group::" + std::to_string(t.cta_group) + ".sync.aligned.b32 " + taddr_var + ", " +
+           std::to_string(t.num_cols) + ";";
+}
+inline std::string tmem_commit_ptx(const Tmem& t, const std::string& mbar_var) {
+    return "tcgen05.commit.cta_group::" + std::to_string(t.cta_group) + ".mbarrier::arrive::one.shared::cluster.b64 [" + mbar_var + "];";
+}
+inline std::string tmem_commit_mask_ptx(const Tmem& t, const std::string& mbar_var, int cta_mask) {
+    return "tcgen05.commit.cta_group::" + std::to_string(t.cta_group) + ".mbarrier::arrive::one.multicast::cluster.shared::cluster.b64 [" +
+           mbar_var + "], " + std::to_string(cta_mask) + ";";
+}
+enum AccumLoc { AccRegisters = 0, AccTensorMem = 1 };
+struct TileOp { TiledMma tiled_mma; int accum_loc; bool has_tmem; Tmem tmem; bool double_buf; };
+inline TileOp tile_op_make(const TiledMma& tm, int accum_loc, const Tmem* tmem, bool double_buf = false) {
+    if (accum_loc == AccTensorMem && !tmem) throw SpecError("TensorMem requires a tmem descriptor");
+    return TileOp{tm, accum_loc, tmem != nullptr, tmem ? *tmem : Tmem{1, 0, 0}, double_buf};
+}
+inline bool tile_op_is_tmem(const TileOp& t) { return t.accum_loc == AccTensorMem; }
+inline bool tile_op_is_wgmma(const TileOp& t) { return mma_atom_is_wgmma(t.tiled_mma.atom); }
+inline i64 tile_op_accum_elems_per_thread(const TileOp& t) { return tiled_mma_partition_c(t.tiled_mma); }
+inline std::string tile_op_emit_mma(const TileOp& t, const std::string& a_desc, const std::string& b_desc, bool enable_accum) {
+    if (t.accum_loc == AccRegisters)
+        return "mma.sync.aligned." + mma_atom_emit_cpp(t.tiled_mma.atom) + " acc, " + a_desc + ", " + b_desc + ", acc;";
+    return "tcgen05.mma.cta_group::" + std::to_string(t.has_tmem ? t.tmem.cta_group : 1) + ".kind::mxf16 [tmem_addr], " +
+           a_desc + ", " + b_desc + ", [i_desc], " + (enable_accum ? "1" : "0") + ";";
+}
+inline std::string tile_op_emit_commit(const TileOp& t, const std::string& mbar_var, int cta_mask) {
+    if (t.accum_loc == AccRegisters || !t.has_tmem) return "";
+    return cta_mask > 1 ? tmem_commit_mask_ptx(t.tmem, mbar_var, cta_mask) : tmem_commit_ptx(t.tmem, mbar_var);
+}
+inline std::string tile_op_emit_accum_decl(const TileOp& t, const std::string& var) {
+    if (t.accum_loc == AccTensorMem) return "";
+    const i64 n = tile_op_accum_elems_per_thread(t);
+    std::string zeros;
+    for (i64 i = 0; i < n; ++i) zeros += (i ? ", 0.0f" : "0.0f");
+    return "float " + var + "[" + std::to_string(n) + "] = {" + zeros + "};";
+}
+inline std::string tile_op_emit_tmem_alloc(const TileOp& t, const std::string& smem_var) { return t.has_tmem ? tmem_alloc_ptx(t.tmem, smem_var) : ""; }
+inline std::string tile_op_emit_tmem_dealloc(const TileOp& t, const std::string& taddr_var) { return t.has_tmem ? tmem_dealloc_ptx(t.tmem, taddr_var) : ""; }
 // ---------------------------------------------------------------- Tile_io (lib/pipeline/tile_io.ml:19-127)
 // The third tag is the reference's SM100 strategy (its name there is "TMA multicast"); here it means
 // "CTA pair, each CTA loads its own rows of A and its own half of B", which moves the same bytes.

@@ -138,17 +138,33 @@ def test_needs_scales_and_k_multiple(torch_cuda):
         plan.run_scaled(x, x, c, s, s, None, 1.0, 256, 256, 192)
 
 
-@pytest.mark.parametrize("knob,value", [("TESSERAE_FP8_SPLIT", "0"), ("TESSERAE_FP8_PROMO_WARPS", "16")])
-def test_structure_variants_agree(torch_cuda, knob, value, monkeypatch):
+@pytest.mark.parametrize("tuning", ["FP8_SPLIT=0", "FP8_PROMO_WARPS=16", "FP8_FMA2=0", "FP8_XPIPE=0"])
+def test_structure_variants_agree(torch_cuda, tuning):
     """The kernel's structural variants (one 256-wide MMA chain instead of two 128-wide ones; sixteen promotion warps
-    instead of eight) are other schedules of the same arithmetic: per K block the same fp32 partial product, scaled
+    instead of eight; scalar instead of packed-pair multiply-adds; each K block's first tensor-memory load after instead
+    of before the previous block's last multiply-adds) are other schedules of the same arithmetic: per K block the same fp32 partial product, scaled
     and added in the same order.  Their outputs must equal the default build's bit for bit."""
     m, n, k = 640, 768, 1024
     p = O.make_fp8_problem(m, n, k, seed=260)
     want = run_scaled(torch_cuda, plan_for(2, 256), p, m, n, k)
-    monkeypatch.setenv(knob, value)                  # read when the plan is created
-    variant = api.GemmPlan(api.KernelSpec(name="gemm_fp8blk_cg2_n256_variant_" + value, elem=api.F8E4M3, tile=(128, 256, 128),
-                                          cta_group=2, out_elem=api.BF16, scale_mode=api.SCALE_FP8_BLOCK))
+    variant = api.GemmPlan(api.KernelSpec(name="gemm_fp8blk_cg2_n256_variant", elem=api.F8E4M3, tile=(128, 256, 128),
+                                          cta_group=2, out_elem=api.BF16, scale_mode=api.SCALE_FP8_BLOCK, tuning=tuning))
     got = run_scaled(torch_cuda, variant, p, m, n, k)
     variant.close()
     assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("m,n,k", [(384, 512, 640), (4608, 2048, 1024)])
+def test_host_buffer_entry_point_equals_device_call(torch_cuda, m, n, k):
+    """tesserae_gemm_run_scaled_host (operands, scale tables up; C back, inside the call; the larger case takes the
+    chunked pipeline with a ragged last chunk) against the device-pointer call on the same inputs: bit-equal."""
+    t = torch_cuda
+    p = O.make_fp8_problem(m, n, k, seed=270)
+    plan = plan_for(2, 256)
+    want = run_scaled(t, plan, p, m, n, k)
+    pin = lambda x: t.from_numpy(np.ascontiguousarray(x)).pin_memory()
+    qa, qb, sa, sb = pin(p["qa"]), pin(p["qb"]), pin(p["sa"]), pin(p["sb"])
+    c = t.full((m, n), float("nan"), dtype=t.bfloat16).pin_memory()
+    plan.run_scaled_host(qa, qb, c, sa, sb, None, 1.0, m, n, k)
+    assert plan.status() == 0
+    assert np.array_equal(c.float().numpy(), want)

@@ -109,3 +109,60 @@ def test_k_must_be_a_stage_multiple(torch_cuda):
     c = t.zeros(256, 256, dtype=t.bfloat16, device="cuda")
     with pytest.raises(api.TesseraeError, match="multiple of 256"):
         plan_for(2, 256).run_scaled(x, x, c, x, x, None, 1.0, 256, 256, 384)
+
+
+def test_config4_full_size(torch_cuda):
+    """NVFP4 GEMM at the full size of config 4 (M=16384, N=28672, K=8192; N(0,1) sources, seed 3).  The sources
+    are drawn on the GPU and quantised by the library's GPU quantisers; the check reads the quantised bytes back
+    and dequantises them with the oracle: sampled entries in fp64, and the row-sum identity
+    sum_n C[m,n] = a[m,:] . sum_n b[n,:] over the whole output."""
+    from helpers import fullsize as F
+    t = torch_cuda
+    m, n, k = 16384, 28672, 8192
+    s = t.cuda.current_stream().cuda_stream
+    ws4 = t.zeros(4, dtype=t.uint8, device="cuda")
+    ops = []
+    for rows_, seed in ((m, 3), (n, 1003)):
+        src = F.draw(t, (rows_, k), seed)
+        q = t.empty((rows_, k // 2), dtype=t.uint8, device="cuda")
+        sf = t.zeros((api.nvfp4_scale_bytes(rows_, k),), dtype=t.uint8, device="cuda")
+        g = api.quantize_nvfp4(src, q, sf, ws4, rows_, k, stream=s)
+        del src
+        ops.append((q, sf, g))
+    (qa, sfa, ga), (qb, sfb, gb) = ops
+    c = t.empty((m, n), dtype=t.float32, device="cuda")
+    plan = plan_for(2, 256, api.F32)
+    plan.run_scaled(qa, qb, c, sfa, sfb, None, 1.0, m, n, k, stream=s, global_a=ga, global_b=gb)
+    assert plan.status() == 0
+    rows = [0, 127, 128, 8191, 16383]
+    cols = list(range(0, n, 211)) + [n - 1]
+    a_s = F.nvfp4_rows_from_device(t, qa, sfa, ga, rows, k)
+    b_s = F.nvfp4_rows_from_device(t, qb, sfb, gb, cols, k)
+    want = a_s.astype(np.float64) @ b_s.astype(np.float64).T
+    got = c[rows][:, cols].cpu().numpy()
+    rms = float(np.sqrt(np.mean(want ** 2)))
+    assert np.max(np.abs(got - want) / np.maximum(np.abs(want), rms / 128)) <= TOL_NVFP4
+    colsum = np.zeros(k, dtype=np.float64)
+    for _, blk in F.nvfp4_all_from_device(t, qb, sfb, gb, n, k):
+        colsum += blk.astype(np.float64).sum(axis=0)
+    got_rowsum = c.double().sum(dim=1).cpu().numpy()
+    want_rowsum = np.empty(m, dtype=np.float64)
+    for r0, blk in F.nvfp4_all_from_device(t, qa, sfa, ga, m, k):
+        want_rowsum[r0:r0 + len(blk)] = blk.astype(np.float64) @ colsum
+    assert np.max(np.abs(got_rowsum - want_rowsum)) <= 1e-3 * float(np.sqrt(np.mean(want_rowsum ** 2)))
+
+
+@pytest.mark.parametrize("m,n,k", [(384, 512, 1024), (4608, 1024, 1024)])
+def test_host_buffer_entry_point_equals_device_call(torch_cuda, m, n, k):
+    """tesserae_gemm_run_scaled_host (operands and chunked scale tables up; C back, inside the call; the larger case
+    takes the chunked pipeline with a ragged last chunk) against the device-pointer call: bit-equal."""
+    t = torch_cuda
+    p = O.make_nvfp4_problem(m, n, k, seed=370)
+    plan = plan_for(2, 256)
+    want = run(t, plan, p, m, n, k)
+    pin = lambda x: t.from_numpy(np.ascontiguousarray(x)).pin_memory()
+    qa, qb, sfa, sfb = pin(p["qa"]), pin(p["qb"]), pin(p["sfa"]), pin(p["sfb"])
+    c = t.full((m, n), float("nan"), dtype=t.bfloat16).pin_memory()
+    plan.run_scaled_host(qa, qb, c, sfa, sfb, None, 1.0, m, n, k, global_a=p["ga"], global_b=p["gb"])
+    assert plan.status() == 0
+    assert np.array_equal(c.float().numpy(), want)

@@ -132,3 +132,38 @@ def test_scatter_epilogue_matches_plain_partial(torch_cuda, plan_f32):
     with pytest.raises(api.TesseraeError, match="multiple of 128"):
         scat.ksplit_scatter(a, b, [d.data_ptr() for d in dst], 100, m, n, k)
     scat.close()
+
+
+def test_config5_full_size(torch_cuda, plan_f32):
+    """The whole K-split GEMM of config 5 on one GPU: M=N=8192, K=131072 (U[-0.5,0.5), seed 4, drawn on the GPU),
+    four K slices of 32768 into fp32 partials, then sum + bf16 cast.  Sampled entries of the bf16 output in fp64
+    (tolerance 1e-2), the row-sum identity sum_n C[m,n] = a[m,:] . sum_n b[n,:] on the summed fp32 partials, and
+    the bf16 output must be exactly the rounded sum of the partials."""
+    from helpers import fullsize as F
+    t = torch_cuda
+    m = n = 8192
+    k, splits = 131072, 4
+    a = F.draw(t, (m, k), 4, "uniform", 0.5).to(t.bfloat16)
+    b = F.draw(t, (n, k), 1004, "uniform", 0.5).to(t.bfloat16)
+    nbytes = api.ksplit_scratch_bytes(m, n, splits)
+    scratch = t.empty(nbytes, dtype=t.uint8, device="cuda")
+    c = t.empty((m, n), dtype=t.bfloat16, device="cuda")
+    plan_f32.ksplit_run(a, b, c, scratch, nbytes, m, n, k, splits, stream=t.cuda.current_stream().cuda_stream)
+    assert plan_f32.status() == 0
+    rows, cols = [0, 255, 4096, 8191], list(range(0, n, 211)) + [n - 1]
+    want = a[rows].double() @ b[cols].double().T                      # fp64 on the device: 4 x 40 x 131072 products
+    got = c[rows][:, cols].double()
+    rms = float(want.pow(2).mean().sqrt())
+    rel = ((got - want).abs() / want.abs().clamp_min(rms / 128)).max()
+    assert float(rel) <= 1e-2, float(rel)
+    parts = scratch.view(t.float32).reshape(splits, m, n)
+    total = parts[0].double()
+    for p_ in range(1, splits):
+        total += parts[p_].double()
+    # the cast pass sums the partials in slice order in fp32 and rounds once
+    fp32_sum = ((parts[0] + parts[1]) + parts[2]) + parts[3]
+    assert t.equal(c, fp32_sum.to(t.bfloat16))
+    colsum = b.double().sum(dim=0)                                    # host-independent fp64 reduction of B
+    want_rowsum = (a.double() @ colsum).cpu().numpy()
+    got_rowsum = total.sum(dim=1).cpu().numpy()
+    assert np.max(np.abs(got_rowsum - want_rowsum)) <= 1e-3 * float(np.sqrt(np.mean(want_rowsum ** 2)))

@@ -197,3 +197,95 @@ def test_kernel_desc_and_lower(goldens):
     for e in goldens["lower_errors"]:
         with pytest.raises(ValueError, match=e["expect_kind"]):
             L.lower_sm100("k", e["elem"], 128, 256, 64)
+
+
+def test_memspace(goldens):
+    g = goldens["memspace"]
+    for name, want in g["names"].items():
+        assert name in L.SPACES and name == want
+    for src, dst, want in g["can_transfer"]:
+        assert L.memspace_can_transfer(src, dst) is want, (src, dst)
+    assert not L.memspace_can_transfer("tensor", "global") and L.memspace_can_transfer("tensor", "tensor")
+
+
+def test_mma_and_copy_atoms(goldens):
+    g = goldens["mma_atom"]
+    for name, want in g["shape"]:
+        a = L.mma_atom(name)
+        assert [a["m"], a["n"], a["k"]] == want
+    for name, want in g["thread_count"]:
+        assert L.mma_atom_thread_count(L.mma_atom(name)) == want
+    for name, want in g["is_wgmma"]:
+        assert L.mma_atom_is_wgmma(L.mma_atom(name)) is want
+    for name, am, bm, want in g["emit_cpp"]:
+        assert L.mma_atom_emit_cpp(L.mma_atom(name, am, bm)) == want
+    g = goldens["copy_atom"]
+    for kind, elem, want in g["bulk_bytes"]:
+        assert L.copy_atom(kind, elem)["bulk_bytes"] == want
+    for kind, elem, want in g["vec_width"]:
+        assert L.copy_atom(kind, elem)["vec_width"] == want
+    for key, fn in (("is_async", L.copy_atom_is_async), ("is_tma", L.copy_atom_is_tma), ("requires_mbar", L.copy_atom_requires_mbar)):
+        for kind, elem, want in g[key]:
+            assert fn(L.copy_atom(kind, elem)) is want, (key, kind)
+    for kind, elem, parts in g["emit_cpp"]:
+        assert L.copy_atom_emit_cpp(L.copy_atom(kind, elem)) == "".join(parts)
+
+
+def _lay(x):
+    return L.Layout(to_modes(x[0]), to_modes(x[1]))
+
+
+def test_tiled_atoms(goldens):
+    g = goldens["tiled_mma"]
+    for c in g["cases"]:
+        t = L.tiled_mma_make(L.mma_atom(c["atom"]), _lay(c["thread_layout"]), _lay(c["warp_layout"]), to_modes(c["tiler_mn"]))
+        assert L.tiled_mma_thread_count(t) == c["thread_count"] and L.tiled_mma_warp_count(t) == c["warp_count"]
+        assert list(L.tiled_mma_tile_shape_mnk(t)) == c["tile_mnk"]
+        assert L.layout_size(L.tiled_mma_partition(t, "c")) == c["partition_c_size"]
+    e = g["error"]
+    with pytest.raises(ValueError, match=e["expect"]):
+        L.tiled_mma_make(L.mma_atom(e["atom"]), _lay(e["thread_layout"]), _lay(e["warp_layout"]), to_modes(e["tiler_mn"]))
+    g = goldens["tiled_copy"]
+    for c in g["cases"]:
+        t = L.tiled_copy_make(L.copy_atom(c["kind"], c["elem"]), _lay(c["thread_layout"]), _lay(c["val_layout"]))
+        assert L.layout_size(t["thread_layout"]) == c["thread_count"]
+        assert L.layout_size(t["val_layout"]) == c["elements_per_thread"]
+        assert L.tiled_copy_tile_size(t) == c["tile_size"]
+        assert L.copy_atom_is_tma(t["atom"]) is c["is_tma"] and L.copy_atom_requires_mbar(t["atom"]) is c["requires_mbar"]
+    p = g["partition"]
+    t = L.tiled_copy_make(L.copy_atom(p["kind"], p["elem"]), _lay(p["thread_layout"]), _lay(p["val_layout"]))
+    assert L.layout_size(L.tiled_copy_partition(t, _lay(p["layout"]))) == p["size"]
+    e = g["error"]
+    with pytest.raises(ValueError, match=e["expect"]):
+        L.tiled_copy_make(L.copy_atom(e["kind"], e["elem"]), _lay(e["thread_layout"]), _lay(e["val_layout"]))
+
+
+def _oracle_tile_op(o):
+    tm = L.tiled_mma_make(L.mma_atom(o["atom"]), _lay(o["thread_layout"]), _lay(o["warp_layout"]), to_modes(o["tiler_mn"]))
+    tmem = L.tmem_make(o["tmem"]["cta_group"], o["tmem"]["num_cols"], o["tmem"]["num_rows"]) if o["tmem"] else None
+    return L.tile_op_make(tm, o["accum"], tmem, o["double_buf"])
+
+
+def test_tile_op(goldens):
+    g = goldens["tile_op"]
+    ops = {k: _oracle_tile_op(v) for k, v in g["ops"].items()}
+    for k, want in g["is_tmem"].items():
+        assert L.tile_op_is_tmem(ops[k]) is want
+    for k, want in g["is_wgmma"].items():
+        assert L.tile_op_is_wgmma(ops[k]) is want
+    for k, want in g["double_buf"].items():
+        assert ops[k]["double_buf"] is want
+    for k, want in g["accum_elems_per_thread"].items():
+        assert L.tile_op_accum_elems_per_thread(ops[k]) == want
+    decl = L.tile_op_emit_accum_decl(ops["sm80"], "acc")
+    assert all(x in decl for x in g["accum_decl"]["sm80_contains"]) and decl == "float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};"
+    assert L.tile_op_emit_accum_decl(ops["sm100"], "acc") == g["accum_decl"]["sm100"]
+    for k, want in g["emit_mma_contains"].items():
+        assert want in L.tile_op_emit_mma(ops[k], "a_desc", "b_desc", False)
+    assert L.tile_op_emit_commit(ops["sm80"], "mbar", 0) == g["emit_commit"]["sm80_mask0"]
+    assert all(x in L.tile_op_emit_commit(ops["sm100"], "mbar", 3) for x in g["emit_commit"]["sm100_mask3_contains"])
+    assert L.tile_op_emit_tmem_alloc(ops["sm80"], "tmem_addr") == g["tmem_alloc"]["sm80"]
+    assert g["tmem_alloc"]["sm100_contains"] in L.tile_op_emit_tmem_alloc(ops["sm100"], "tmem_addr")
+    assert g["tmem_dealloc_contains"]["sm100"] in L.tile_op_emit_tmem_dealloc(ops["sm100"], "taddr")
+    with pytest.raises(ValueError, match="TensorMem requires a tmem descriptor"):
+        L.tile_op_make(ops["sm80"]["tiled_mma"], "TensorMem", None)

@@ -224,3 +224,121 @@ def test_hardware_descriptors():
     i = lib.tesserae_umma_instr_desc(api.BF16, 256, 256)
     assert (i >> 4) & 3 == 1 and (i >> 7) & 7 == 1 and (i >> 10) & 7 == 1 and (i >> 17) & 63 == 32 and (i >> 24) & 31 == 16
     assert (i >> 15) & 3 == 0   # both operands K-major
+
+
+def _size(pair):
+    n = 1
+    for x in flat(pair[0]):
+        n *= x
+    return n
+
+
+def test_goldens_memspace_and_atoms(goldens):
+    g = goldens["memspace"]
+    for name, want in g["names"].items():
+        assert api.memspace_name(name) == want
+    for src, dst, want in g["can_transfer"]:
+        assert api.memspace_can_transfer(src, dst) is want, (src, dst)
+    g = goldens["mma_atom"]
+    for name, want in g["shape"]:
+        a = api.mma_atom(name)
+        assert [a.m, a.n, a.k] == want
+    for name, want in g["thread_count"]:
+        assert api.mma_atom_thread_count(api.mma_atom(name)) == want
+    for name, want in g["is_wgmma"]:
+        assert api.mma_atom_is_wgmma(api.mma_atom(name)) is want
+    for name, am, bm, want in g["emit_cpp"]:
+        assert api.mma_atom_emit_cpp(api.mma_atom(name, am, bm)) == want
+    g = goldens["copy_atom"]
+    for kind, elem, want in g["bulk_bytes"]:
+        assert api.copy_atom(kind, elem).bulk_bytes == want
+    for kind, elem, want in g["vec_width"]:
+        assert api.copy_atom(kind, elem).vec_width == want
+    for key, fn in (("is_async", api.copy_atom_is_async), ("is_tma", api.copy_atom_is_tma),
+                    ("requires_mbar", api.copy_atom_requires_mbar)):
+        for kind, elem, want in g[key]:
+            assert fn(api.copy_atom(kind, elem)) is want, (key, kind)
+    for kind, elem, parts in g["emit_cpp"]:
+        assert api.copy_atom_emit_cpp(api.copy_atom(kind, elem)) == "".join(parts)
+
+
+def test_goldens_tiled_atoms_and_tile_op(goldens):
+    g = goldens["tiled_mma"]
+    for c in g["cases"]:
+        t = api.tiled_mma(api.mma_atom(c["atom"]), _size(c["thread_layout"]), _size(c["warp_layout"]), *c["tiler_mn"])
+        assert (t.thread_count, t.warp_count) == (c["thread_count"], c["warp_count"])
+        assert [t.tile_m, t.tile_n, t.tile_k] == c["tile_mnk"] and t.partition_c == c["partition_c_size"]
+    e = g["error"]
+    with pytest.raises(ValueError, match=e["expect"]):
+        api.tiled_mma(api.mma_atom(e["atom"]), _size(e["thread_layout"]), _size(e["warp_layout"]), *e["tiler_mn"])
+    g = goldens["tiled_copy"]
+    for c in g["cases"]:
+        t = api.tiled_copy(api.copy_atom(c["kind"], c["elem"]), _size(c["thread_layout"]), _size(c["val_layout"]))
+        assert (t.thread_count, t.elements_per_thread, t.tile_size) == (c["thread_count"], c["elements_per_thread"], c["tile_size"])
+        assert bool(t.is_tma) is c["is_tma"] and bool(t.requires_mbar) is c["requires_mbar"]
+    p = g["partition"]
+    shape, _ = api.tiled_copy_partition(_size(p["thread_layout"]), *fl(p["layout"]))
+    assert shape == p["size"]
+    e = g["error"]
+    with pytest.raises(ValueError, match=e["expect"]):
+        api.tiled_copy(api.copy_atom(e["kind"], e["elem"]), _size(e["thread_layout"]), _size(e["val_layout"]))
+
+    g = goldens["tile_op"]
+
+    def make(o):
+        tmem = (o["tmem"]["cta_group"], o["tmem"]["num_cols"], o["tmem"]["num_rows"]) if o["tmem"] else None
+        return api.tile_op(api.mma_atom(o["atom"]), _size(o["thread_layout"]), _size(o["warp_layout"]), *o["tiler_mn"],
+                           o["accum"], tmem, o["double_buf"])
+    ops = {k: make(v) for k, v in g["ops"].items()}
+    for k, want in g["is_tmem"].items():
+        assert api.tile_op_is_tmem(ops[k]) is want
+    for k, want in g["is_wgmma"].items():
+        assert api.tile_op_is_wgmma(ops[k]) is want
+    for k, want in g["accum_elems_per_thread"].items():
+        assert api.tile_op_accum_elems_per_thread(ops[k]) == want
+    decl = api.tile_op_emit(ops["sm80"], "accum_decl", "acc")
+    assert all(x in decl for x in g["accum_decl"]["sm80_contains"])
+    assert api.tile_op_emit(ops["sm100"], "accum_decl", "acc") == g["accum_decl"]["sm100"]
+    for k, want in g["emit_mma_contains"].items():
+        assert want in api.tile_op_emit(ops[k], "mma", "a_desc", "b_desc", 0)
+    assert api.tile_op_emit(ops["sm80"], "commit", "mbar", "", 0) == g["emit_commit"]["sm80_mask0"]
+    assert all(x in api.tile_op_emit(ops["sm100"], "commit", "mbar", "", 3) for x in g["emit_commit"]["sm100_mask3_contains"])
+    assert api.tile_op_emit(ops["sm80"], "tmem_alloc", "tmem_addr") == g["tmem_alloc"]["sm80"]
+    assert g["tmem_alloc"]["sm100_contains"] in api.tile_op_emit(ops["sm100"], "tmem_alloc", "tmem_addr")
+    assert g["tmem_dealloc_contains"]["sm100"] in api.tile_op_emit(ops["sm100"], "tmem_dealloc", "taddr")
+    with pytest.raises(ValueError, match="TensorMem requires a tmem descriptor"):
+        api.tile_op(api.mma_atom("sm100_64x64x16_f32f16f16f32"), 128, 1, 64, 64, "TensorMem", None)
+
+
+def test_atoms_product_equals_oracle_everywhere():
+    """Every constructor x major pair, every copy kind x element, and the Tile_op text of both accumulator
+    locations: the C++ model behind the C ABI against the independent Python restatement, string for string."""
+    for name in api.MMA_ATOM_IDS:
+        for am in ("RowMajor", "ColMajor"):
+            for bm in ("RowMajor", "ColMajor"):
+                pa, oa = api.mma_atom(name, am, bm), L.mma_atom(name, am, bm)
+                assert api.mma_atom_emit_cpp(pa) == L.mma_atom_emit_cpp(oa)
+                assert api.mma_atom_thread_count(pa) == L.mma_atom_thread_count(oa)
+                assert [pa.m, pa.n, pa.k] == [oa["m"], oa["n"], oa["k"]]
+    for kind in api.COPY_KINDS:
+        for elem in api.ELEMS:
+            pa, oa = api.copy_atom(kind, elem), L.copy_atom(kind, elem)
+            assert (pa.vec_width, pa.bulk_bytes) == (oa["vec_width"], oa["bulk_bytes"]), (kind, elem)
+            assert api.copy_atom_emit_cpp(pa) == L.copy_atom_emit_cpp(oa)
+            assert api.memspace_name(["global", "shared", "register", "tensor"][pa.src_space]) == oa["src"]
+    for src in api.SPACES:
+        for dst in api.SPACES:
+            assert api.memspace_can_transfer(src, dst) is L.memspace_can_transfer(src, dst), (src, dst)
+    for name, accum, tmem in (("sm80_16x8x16_f32f16f16f32", "Registers", None), ("sm100_128x128x16_f32f16f16f32", "TensorMem", (2, 512, 128)),
+                              ("sm100_64x64x32_s32s8s8s32", "TensorMem", (1, 64, 128))):
+        threads = 32 if name.startswith("sm80") else 128
+        po = api.tile_op(api.mma_atom(name), threads, 1, 64, 64, accum, tmem)
+        otm = L.tiled_mma_make(L.mma_atom(name), L.Layout(threads, 1), L.Layout(1, 0), (64, 64))
+        oo = L.tile_op_make(otm, accum, L.tmem_make(*tmem) if tmem else None)
+        assert api.tile_op_emit(po, "mma", "da", "db", 1) == L.tile_op_emit_mma(oo, "da", "db", True)
+        for mask in (0, 1, 3):
+            assert api.tile_op_emit(po, "commit", "bar", "", mask) == L.tile_op_emit_commit(oo, "bar", mask)
+        assert api.tile_op_emit(po, "accum_decl", "acc") == L.tile_op_emit_accum_decl(oo, "acc")
+        assert api.tile_op_emit(po, "tmem_alloc", "slot") == L.tile_op_emit_tmem_alloc(oo, "slot")
+        assert api.tile_op_emit(po, "tmem_dealloc", "addr") == L.tile_op_emit_tmem_dealloc(oo, "addr")
+        assert api.tile_op_accum_elems_per_thread(po) == L.tile_op_accum_elems_per_thread(oo)
