@@ -178,7 +178,9 @@ def workload_config(name, w, gpus, exchange="fused"):
     else:
         sharding = ("single GPU: fp32 partials of K slices of 32768 + sum and bf16 cast" if gpus == 1 else
                     f"K-split over {gpus} GPUs, reduce-scatter of the fp32 partials "
-                    + ("fused into the GEMM's stores over NVLink peer memory" if exchange == "fused" else "by NCCL") + ", bf16 cast")
+                    + ("fused into the GEMM's epilogue: tiles added into the owner's buffer over NVLink (TMA reduce)" if exchange == "reduce"
+                       else "fused into the GEMM's stores over NVLink peer memory, summed by the owner" if exchange == "fused"
+                       else "by NCCL") + ", bf16 cast")
         shape = {"m": m, "n_total": n, "k_per_gpu": k // gpus, "k": k}
     return dict({"workload": name, "tile": w["tile"], "sharding": sharding,
                  "epilogue": "alpha=1" + (" + bf16 bias[n]" if w["bias"] else "") + f" -> {w['out']}",
@@ -303,12 +305,13 @@ class Workload:
         self.c = t.empty((rows, self.n), dtype=t.bfloat16, device=self.dev)
         self.c_host = t.empty((rows, self.n), dtype=t.bfloat16).pin_memory()
         fused = self.world > 1 and self.exchange == "fused"
-        self.plan = api.GemmPlan(api.KernelSpec(name="gemm_bf16_cg2_f32_scatter" if fused else "gemm_bf16_cg2_f32_b0",
+        reduce_ = self.world > 1 and self.exchange == "reduce"
+        self.plan = api.GemmPlan(api.KernelSpec(name="gemm_bf16_cg2_f32_scatter" if fused else
+                                                "gemm_bf16_cg2_f32_scatter_add" if reduce_ else "gemm_bf16_cg2_f32_b0",
                                                 elem=api.BF16, tile=(128, 256, 64), cta_group=2, out_elem=api.F32,
-                                                scatter=int(fused)))
+                                                scatter=1 if fused else 2 if reduce_ else 0))
         nbytes = self.partial.numel() * 4
         self.launches_per_step = 2
-        self.ev = [t.cuda.Event(enable_timing=True) for _ in range(3)]
         if fused:
             # Exchange fused into the GEMM: every tile's TMA store lands in its owner's staging slot
             # stag[buffer][source rank] over NVLink while the tensor cores run on; one barrier, then each
@@ -321,19 +324,53 @@ class Workload:
             slot = rows * self.n * 4
             self._symm, self._it = (stag, hdl), 0
 
-            def step(record=False):
+            def step(ev=None):
                 buf = self._it & 1
                 self._it += 1
                 dst = [hdl.buffer_ptrs[g] + (buf * self.world + self.rank) * slot for g in range(self.world)]
-                if record:
-                    self.ev[0].record()
+                if ev:
+                    ev[0].record()
                 self.plan.ksplit_scatter(self.a, self.b, dst, rows, self.m, self.n, self.k, stream=self.stream)
-                if record:
-                    self.ev[1].record()
+                if ev:
+                    ev[1].record()
                 hdl.barrier(channel=0)
                 api.reduce_cast_bf16(stag[buf], self.world, rows * self.n, self.c, rows * self.n, stream=self.stream)
-                if record:
-                    self.ev[2].record()
+                if ev:
+                    ev[2].record()
+            self.step = step
+            self._finish_ksplit()
+            return
+
+        if reduce_:
+            # Exchange and sum fused into the GEMM: every tile is ADDED (TMA reduce, fp32 add in the owner's memory
+            # system) into the owner's one M/G x N buffer; one barrier; the owner casts.  No staging per source, no
+            # sum pass.  Two buffers: the one a step has cast is cleared right away and is written again only two
+            # steps later, after every rank has passed the barrier of the step in between.
+            import torch.distributed._symmetric_memory as symm
+            self.partial = None
+            acc = symm.empty((2, rows, self.n), dtype=t.float32, device=self.dev)
+            hdl = symm.rendezvous(acc, dist.group.WORLD.group_name)
+            acc.zero_()
+            t.cuda.synchronize()
+            hdl.barrier(channel=0)
+            self._symm, self._it = (acc, hdl), 0
+            half = rows * self.n * 4
+
+            def step(ev=None):
+                buf = self._it & 1
+                self._it += 1
+                dst = [hdl.buffer_ptrs[g] + buf * half for g in range(self.world)]
+                if ev:
+                    ev[0].record()
+                self.plan.ksplit_scatter(self.a, self.b, dst, rows, self.m, self.n, self.k, stream=self.stream)
+                if ev:
+                    ev[1].record()
+                hdl.barrier(channel=0)
+                api.reduce_cast_bf16(acc[buf], 1, 0, self.c, rows * self.n, stream=self.stream)
+                acc[buf].zero_()
+                if ev:
+                    ev[2].record()
+            self.launches_per_step = 3
             self.step = step
             self._finish_ksplit()
             return
@@ -347,18 +384,18 @@ class Workload:
             self.mine = self.partial
             nbytes = self.partial.numel() * 4
 
-        def step(record=False):
-            if record:
-                self.ev[0].record()
+        def step(ev=None):
+            if ev:
+                ev[0].record()
             self.plan.ksplit_partials(self.a, self.b, self.partial, nbytes, self.m, self.n, self.k, slices, stream=self.stream)
-            if record:
-                self.ev[1].record()
+            if ev:
+                ev[1].record()
             if self.world > 1:
                 dist.reduce_scatter_tensor(self.mine, self.partial, op=dist.ReduceOp.SUM)
             api.reduce_cast_bf16(self.mine, slices, self.m * self.n if slices > 1 else 0, self.c, self.c.numel(),
                                  stream=self.stream)
-            if record:
-                self.ev[2].record()
+            if ev:
+                ev[2].record()
         self.launches_per_step = slices + 1
         self.step = step
         self._finish_ksplit()
@@ -478,9 +515,15 @@ def measure(name, w, rank, local_rank, world, dev, args, exchange="fused", extra
     sampler = ClockSampler(local_rank)
     sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # K-split: every timed step also records (start, GEMM done, exchange + cast done), so that the compute and the
+    # exchange shares come from the same steps, under the same clocks, as the step time itself
+    marks = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)] if w["kind"] == "ksplit" else None
     e0.record()
-    for _ in range(args.steps):
-        wl.step()
+    for i in range(args.steps):
+        if marks:
+            wl.step(marks[i])
+        else:
+            wl.step()
     e1.record()
     sync_all()
     clocks = sampler.stop()
@@ -499,13 +542,10 @@ def measure(name, w, rank, local_rank, world, dev, args, exchange="fused", extra
         burst_ms.append(b0.elapsed_time(b1))
     sync_all()
 
-    # ---- K-split: compute and communication separately (one recorded step)
+    # ---- K-split: compute and communication separately, means over the timed steps
     split = None
-    if w["kind"] == "ksplit":
-        wl.step(record=True)
-        torch.cuda.synchronize()
-        split = [wl.ev[0].elapsed_time(wl.ev[1]), wl.ev[1].elapsed_time(wl.ev[2])]
-        sync_all()
+    if marks:
+        split = [sum(m[0].elapsed_time(m[1]) for m in marks) / len(marks), sum(m[1].elapsed_time(m[2]) for m in marks) / len(marks)]
 
     # ---- end to end from pinned host buffers
     wl.e2e_step()
@@ -626,8 +666,9 @@ def main():
                     help="also measure fp8_block, nvfp4 and bf16_ksplit in the same process (default: all for the "
                          "headline workload, none otherwise)")
     ap.add_argument("--sustained-seconds", type=float, default=1.0)
-    ap.add_argument("--ksplit-exchange", default="fused", choices=["fused", "nccl"],
-                    help="K-split at 2+ GPUs: scatter fused into the GEMM's stores over peer memory, or NCCL reduce-scatter")
+    ap.add_argument("--ksplit-exchange", default="reduce", choices=["reduce", "fused", "nccl"],
+                    help="K-split at 2+ GPUs: tiles added into the owner's buffer by the GEMM's own stores (reduce), stored "
+                         "to per-source slots and summed by the owner (fused), or NCCL reduce-scatter of plain partials")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
     rank = int(os.environ.get("RANK", "0"))
@@ -699,24 +740,29 @@ def main():
                 continue
             sw = WORKLOADS[name]
             try:
-                srec, swl, _ = measure(name, sw, rank, local_rank, world, dev, args, exchange="fused")
+                srec, swl, _ = measure(name, sw, rank, local_rank, world, dev, args, exchange="reduce")
                 if sw["kind"] == "ksplit" and world > 1:
-                    fused_c = swl.c.clone()
-                    swl.close(); del swl
-                    torch.cuda.empty_cache()
-                    nrec, nwl, _ = measure(name, sw, rank, local_rank, world, dev, args, exchange="nccl")
-                    same = torch.equal(fused_c.view(torch.int16), nwl.c.view(torch.int16))
-                    diff = (fused_c.float() - nwl.c.float()).abs().max()
-                    flags = torch.tensor([0.0 if same else 1.0, float(diff)], dtype=torch.float64, device=dev)
+                    keep = ("value", "ms_per_step", "ksplit", "max_rel_err_vs_oracle_sample", "kernel_status",
+                            "pct_of_nominal_dense_peak")
+                    outs = {"reduce": swl.c.clone()}
+                    for other in ("fused", "nccl"):
+                        swl.close(); del swl
+                        torch.cuda.empty_cache()
+                        orec, swl, _ = measure(name, sw, rank, local_rank, world, dev, args, exchange=other)
+                        outs[other] = swl.c.clone()
+                        srec[other] = {k: orec[k] for k in keep}
+                    flags = []
+                    for x in ("reduce", "fused"):
+                        same = torch.equal(outs[x].view(torch.int16), outs["nccl"].view(torch.int16))
+                        flags += [0.0 if same else 1.0, float((outs[x].float() - outs["nccl"].float()).abs().max())]
+                    flags = torch.tensor(flags, dtype=torch.float64, device=dev)
                     dist.all_reduce(flags, op=dist.ReduceOp.MAX)
-                    srec["nccl"] = {k: nrec[k] for k in ("value", "ms_per_step", "ksplit", "max_rel_err_vs_oracle_sample",
-                                                         "kernel_status", "pct_of_nominal_dense_peak")}
-                    srec["fused_equals_nccl"] = flags[0].item() == 0.0
-                    srec["fused_vs_nccl_max_abs_diff"] = flags[1].item()
-                    srec["fused_vs_nccl_note"] = ("both exchanges sum the same fp32 partials; the fused one adds the source "
-                                                  "ranks' slots in rank order, NCCL in its ring order, so beyond 2 ranks the "
-                                                  "bf16 results may differ in the last place")
-                    swl = nwl
+                    srec["reduce_equals_nccl"], srec["reduce_vs_nccl_max_abs_diff"] = flags[0].item() == 0.0, flags[1].item()
+                    srec["fused_equals_nccl"], srec["fused_vs_nccl_max_abs_diff"] = flags[2].item() == 0.0, flags[3].item()
+                    srec["exchange_note"] = ("all three exchanges sum the same fp32 partials: `reduce` in the order the tiles "
+                                             "arrive at the owner, `fused` in rank order, NCCL in its ring order; with 2 ranks "
+                                             "the sums are equal to the bit, beyond that the bf16 results may differ in the "
+                                             "last place")
                 subs[name] = srec
                 swl.close(); del swl
             except Exception as exc:                       # a sub-record must not take the headline down

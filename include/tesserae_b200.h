@@ -234,7 +234,8 @@ typedef struct tesserae_kernel_spec {
     int out_elem;    /* 0 or TESSERAE_F32: fp32 C (reference); TESSERAE_BF16: bf16 C */
     int has_bias;    /* add bf16 bias[n] in the epilogue */
     int scale_mode;  /* TESSERAE_SCALE_* */
-    int scatter;     /* 1: row-scattered output for tesserae_gemm_ksplit_scatter (unscaled kernels, no bias) */
+    int scatter;     /* row-scattered output for tesserae_gemm_ksplit_scatter (unscaled kernels, fp32 out, no bias):
+                        1 = each tile is stored to the owner's slot, 2 = each tile is added into the owner's buffer */
     /* Optional overrides of the kernel's tuning choices, "NAME=VALUE;NAME=VALUE" (NULL or "" = the defaults).
      * The kernel a plan runs is a function of its spec alone; nothing is read from the environment.  Names:
      *   GROUP_M=1..64          M-tiles per raster group of the persistent tile order
@@ -243,9 +244,6 @@ typedef struct tesserae_kernel_spec {
      *                          4 = stores of C evict_first
      *   FP8_PROMO_WARPS=8|16   block-scaled FP8: promotion warps
      *   FP8_SPLIT=0|1          block-scaled FP8: one MMA chain per tile width / per 128 columns
-     *   FP8_FMA2=0|1           block-scaled FP8: scalar / packed-pair promotion multiply-adds
-     *   FP8_XPIPE=0|1          block-scaled FP8: load each K block's partial product after / before the previous
-     *                          block's last multiply-adds
      * An unknown name or a value out of range fails with IncompatibleTile. */
     const char* tuning;
 } tesserae_kernel_spec;
@@ -471,7 +469,12 @@ int tesserae_gemm_ksplit_run(tesserae_gemm_plan* plan, const void* a, const void
  * rows_per_owner is a multiple of 128 and n_dst * rows_per_owner >= m.  With dst[g] pointing into GPU g's
  * memory (peer mapping of a staging slot reserved for this source GPU) the partial tiles cross NVLink as
  * plain TMA stores while the mainloop runs; after a barrier between the GPUs each owner sums its slots with
- * tesserae_reduce_cast_bf16.  Only stores go to peer memory; every load is local. */
+ * tesserae_reduce_cast_bf16.  Only stores go to peer memory; every load is local.
+ * With scatter = 2 in the spec the tiles are not stored but ADDED (fp32, by the memory system of the GPU that owns
+ * dst[g]; a TMA reduce, still a store-type operation): every source GPU passes the SAME dst[g] for owner g, the
+ * buffers must hold zeros when the first contribution arrives, and after the barrier dst[own] already is the
+ * reduce-scattered fp32 sum, so only tesserae_reduce_cast_bf16 with n_parts = 1 remains.  The contributions of
+ * more than two GPUs meet in no fixed order: the sum may differ in the last place between runs. */
 int tesserae_gemm_ksplit_scatter(tesserae_gemm_plan* plan, const void* a, const void* b, void* const* dst, int n_dst,
                                  int64_t rows_per_owner, int64_t m, int64_t n, int64_t k, void* stream);
 /* tesserae_gemm_ksplit_run without caller scratch and without any allocation.  It has no counterpart in

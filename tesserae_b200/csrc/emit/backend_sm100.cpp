@@ -117,7 +117,11 @@ int derive_config(const tesserae_kernel_spec& ks, KernelConfig* cfg, std::string
     c.out_elem = (ks.out_elem == TESSERAE_BF16) ? TESSERAE_BF16 : TESSERAE_F32;
     c.has_bias = ks.has_bias ? 1 : 0;
     c.scale_mode = ks.scale_mode;
-    c.scatter = ks.scatter ? 1 : 0;
+    c.scatter = (ks.scatter == 1 || ks.scatter == 2) ? ks.scatter : 0;
+    if (ks.scatter != 0 && c.scatter == 0) {
+        if (msg) *msg = "IncompatibleTile: scatter must be 0, 1 (store to per-source slots) or 2 (add into the owner's buffer)";
+        return spec::IncompatibleTile;
+    }
     if (c.scatter && (ks.scale_mode != TESSERAE_SCALE_NONE || ks.has_bias || c.out_elem != TESSERAE_F32)) {
         if (msg) *msg = "IncompatibleTile: scattered output is for unscaled kernels with fp32 output and no bias";
         return spec::IncompatibleTile;
@@ -142,8 +146,6 @@ int derive_config(const tesserae_kernel_spec& ks, KernelConfig* cfg, std::string
             else if (key == "STORE_BUFS") { ok = v >= 2 && v <= 4; c.store_bufs = v; }
             else if (key == "FP8_PROMO_WARPS") { ok = v == 8 || v == 16; want_promo_warps = v; }
             else if (key == "FP8_SPLIT") { ok = v == 0 || v == 1; c.fp8_split = v; }
-            else if (key == "FP8_FMA2") { ok = v == 0 || v == 1; c.fp8_fma2 = v; }
-            else if (key == "FP8_XPIPE") { ok = v == 0 || v == 1; c.fp8_xpipe = v; }
             else { if (msg) *msg = "IncompatibleTile: unknown tuning name '" + key + "'"; return spec::IncompatibleTile; }
             if (!ok) {
                 if (msg) *msg = "IncompatibleTile: tuning value out of range: " + key + "=" + std::to_string(v);
@@ -257,12 +259,10 @@ BackendOutput emit(const KernelConfig& c) {
              fp8 ? "TS_FMT_E4M3" : s8 ? "TS_FMT_S8" : (c.elem == TESSERAE_F16 ? "TS_FMT_F16" : "TS_FMT_BF16"),
              c.out_elem == TESSERAE_F32 ? 1 : 0, c.has_bias, c.promo_warps ? c.promo_warps : 8, c.desc.swizzle.b);
     o.includes = buf;
-    if (c.scatter) o.includes += "#define TS_SCATTER 1\n";
+    if (c.scatter) o.includes += "#define TS_SCATTER " + std::to_string(c.scatter) + "\n";
     if (c.scale_mode == TESSERAE_SCALE_NONE) o.includes += "#define TS_STORE_BUFS " + std::to_string(c.store_bufs) + "\n";
     if (c.scale_mode == TESSERAE_SCALE_FP8_BLOCK) {
         o.includes += std::string("#define TS_FP8_SPLIT ") + (c.fp8_split ? "1\n" : "0\n");
-        o.includes += std::string("#define TS_FP8_FMA2 ") + (c.fp8_fma2 ? "1\n" : "0\n");
-        o.includes += std::string("#define TS_FP8_XPIPE ") + (c.fp8_xpipe ? "1\n" : "0\n");
     }
     o.includes += "#define TS_GROUP_M " + std::to_string(c.group_m) + "\n";
     if (c.scale_mode == TESSERAE_SCALE_NONE) o.includes += "#define TS_L2_HINT " + std::to_string(c.l2_hint) + "\n";

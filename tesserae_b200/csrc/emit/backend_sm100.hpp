@@ -20,14 +20,12 @@ struct KernelConfig {
     int stages = 4;
     int has_bias = 0;
     int scale_mode = TESSERAE_SCALE_NONE;
-    int scatter = 0;         // row-scattered output (dense kernel only)
+    int scatter = 0;         // row-scattered output (dense kernel only): 1 stored to per-source slots, 2 added into the owner's buffer
     int promo_warps = 0;     // promotion warps of the FP8 block-scaled kernel (0 elsewhere)
     int store_bufs = 2;      // dense kernel: staging buffers per epilogue warp (4 when the stores cross NVLink)
     int group_m = 8;         // M-tiles per raster group of the persistent tile order
     int l2_hint = 0;         // dense kernel: bit mask of L2 eviction hints (1 A evict_last, 2 B evict_first, 4 C stores evict_first)
-    int fp8_fma2 = 1;        // FP8 block-scaled: promotion multiply-adds issued as packed pairs
-    int fp8_xpipe = 1;       // FP8 block-scaled: next K block's first tensor-memory load issued before this block's last multiply-adds
-    int fp8_split = 1;       // FP8 block-scaled: one MMA chain and TMEM buffer per 128 columns (else per tile width)
+    int fp8_split = 1;       // FP8 block-scaled: 1 = one MMA chain and TMEM buffer per 128 columns, 0 = per tile width
     int b_box_rows = 128;    // rows of B one TMA load brings (the FP8 block-scaled pair kernel loads B per 128-column MMA group)
     int threads = 192;
     int smem_bytes = 0;      // dynamic shared memory to request

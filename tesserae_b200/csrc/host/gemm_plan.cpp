@@ -486,7 +486,7 @@ int tesserae_gemm_ksplit_scatter(tesserae_gemm_plan* p, const void* a, const voi
     if (!p || !a || !b || !dst) return fail("ksplit_scatter: null argument");
     if (int drc = check_plan_device(p, "ksplit_scatter")) return drc;
     const KernelConfig& cfg = p->cfg;
-    if (!cfg.scatter) return fail("ksplit_scatter: the plan's spec must have scatter = 1");
+    if (!cfg.scatter) return fail("ksplit_scatter: the plan's spec must have scatter = 1 or 2");
     if (n_dst < 1 || n_dst > 8) return fail("ksplit_scatter: n_dst must be in 1..8");
     if (rows_per_owner <= 0 || rows_per_owner % 128 != 0) return fail("ksplit_scatter: rows_per_owner must be a positive multiple of 128");
     if (m <= 0 || n <= 0 || k <= 0 || m > INT32_MAX || n > INT32_MAX || k > INT32_MAX) return fail("ksplit_scatter: bad dimensions");

@@ -40,6 +40,11 @@
 //                    GEMM -> reduce-scatter fusion of the K-split: each GPU's fp32 partial tiles go straight
 //                    to the GPU that owns the rows (plain TMA stores over NVLink), tile by tile, while the
 //                    mainloop continues; the owner then sums its G slots.
+//                    TS_SCATTER 2: the same routing, but each tile is ADDED into the owner's buffer (TMA reduce, fp32
+//                    add at the destination) instead of stored to a per-source slot: all G GPUs add into one
+//                    M/G x N fp32 array per owner, which must hold zeros beforehand; no sum pass follows, only the
+//                    cast.  The order in which the G contributions meet is not fixed, so beyond two GPUs the fp32
+//                    sum can differ in the last place from run to run.
 #pragma once
 
 #ifndef TS_SCATTER
@@ -355,7 +360,11 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
 #if TS_SCATTER
                     if (col0 < (ts_u32)N && row0 < M) {
                         const int owner = row0 / rows_per_owner;       // rows_per_owner is a multiple of 32
+#if TS_SCATTER == 2
+                        ts_tma_reduce_add_2d(&tmap_cs.m[owner], buf, (int)col0, row0 - owner * rows_per_owner);
+#else
                         ts_tma_store_2d(&tmap_cs.m[owner], buf, (int)col0, row0 - owner * rows_per_owner);
+#endif
                     }
 #else
 #if TS_L2_HINT & 4

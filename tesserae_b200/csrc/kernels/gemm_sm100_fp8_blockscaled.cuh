@@ -72,12 +72,6 @@ constexpr ts_u32 kThreads     = 32 * (kFirstPromoWarp + kNumPromoWarps);
 constexpr int    kRegsIssue   = kNumPromoWarps == 8 ? 40 : 32;  // register budgets after the split (per thread)
 constexpr int    kRegsPromo   = kNumPromoWarps == 8 ? 232 : 112;
 constexpr ts_u32 kLdCols      = kNumPromoWarps == 8 ? 32 : 16;  // TMEM columns per load of the promotion loop
-#ifndef TS_FP8_FMA2
-#define TS_FP8_FMA2 1          // promotion multiply-adds issued as packed pairs (fma.rn.f32x2)
-#endif
-#ifndef TS_FP8_XPIPE
-#define TS_FP8_XPIPE 1         // the first tensor-memory load of K block i+1 is issued before the last multiply-adds of block i
-#endif
 #ifndef TS_SCALES_EARLY
 #define TS_SCALES_EARLY 1
 #endif
@@ -346,7 +340,6 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
             const ts_u32 col_in_buf = (half * kWarpCols) % kBufCols;
             ts_u32 p0[kLdCols], p1[kLdCols];      // two TMEM load buffers, used in turn
             // First load of the tile: columns 0..kLdCols-1 of the first K block's partial product.
-#if TS_FP8_XPIPE
             {
                 const ts_u32 unit = it * kHalves + grp;
                 const ts_u32 buf = unit % kNumAcc;
@@ -359,7 +352,6 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
                     ts_tmem_ld(tmem_base + ((quarter * 32u) << 16) + buf * kBufCols + col_in_buf, p0);
                 }
             }
-#endif
 #pragma unroll 1
             for (ts_u32 kb0 = 0; kb0 < nkb && ok; kb0 += kScaleRing) {
 #pragma unroll
@@ -370,18 +362,9 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
                 const float s = alpha * sa_r[j] * __shfl_sync(0xffffffffu, sb_l, (int)(kb & 31u));
                 if (kb + kScaleRing < nkb) sa_r[j] = __ldg(sa_ptr + kb + kScaleRing);
                 const ts_u64 s2 = ts_pack_f32x2(__float_as_uint(s), __float_as_uint(s));
-                (void)s2;
                 const ts_u32 unit = it * kHalves + grp;
                 const ts_u32 buf = unit % kNumAcc;
                 const ts_u32 t_row = tmem_base + ((quarter * 32u) << 16) + buf * kBufCols + col_in_buf;
-#if !TS_FP8_XPIPE
-                if (!ts_mbar_wait(tmem_full_bar + 8 * buf, (unit / kNumAcc) & 1u)) {
-                    if (lane == 0) atomicOr(status, TS_ERR_TIMEOUT_TMEM_FULL);
-                    ok = false; continue;
-                }
-                ts_tc_fence_after();
-                ts_tmem_ld(t_row, p0);
-#endif
                 // kLdCols columns at a time, two register buffers: the load of the next group is in flight while the
                 // multiply-adds of the current one issue.  The buffer goes back to the tensor core as soon as its last
                 // load has landed; the first load of the NEXT K block is then issued in front of this block's last
@@ -398,7 +381,6 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
                             if (TS_CTA_GROUP == 2) ts_mbar_arrive_cluster(leader_tmem_empty + 8 * buf);
                             else                   ts_mbar_arrive(tmem_empty_bar + 8 * buf);
                         }
-#if TS_FP8_XPIPE
                         if (kb + 1 < nkb) {
                             const ts_u32 unit_n = (it + 1) * kHalves + grp;
                             const ts_u32 buf_n = unit_n % kNumAcc;
@@ -411,20 +393,11 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
                                 ts_tmem_ld(tmem_base + ((quarter * 32u) << 16) + buf_n * kBufCols + col_in_buf, p0);
                             }
                         }
-#endif
                     }
 #pragma unroll
                     for (ts_u32 i = 0; i < kLdCols / 2; ++i) {
-#if TS_FP8_FMA2
                         const ts_u64 pp = (c & 1u) ? ts_pack_f32x2(p1[2 * i], p1[2 * i + 1]) : ts_pack_f32x2(p0[2 * i], p0[2 * i + 1]);
                         acc2[(c * kLdCols) / 2 + i] = ts_fma_f32x2(pp, s2, acc2[(c * kLdCols) / 2 + i]);
-#else
-                        float lo, hi;
-                        ts_unpack_f32x2(acc2[(c * kLdCols) / 2 + i], lo, hi);
-                        lo = fmaf(__uint_as_float((c & 1u) ? p1[2 * i] : p0[2 * i]), s, lo);
-                        hi = fmaf(__uint_as_float((c & 1u) ? p1[2 * i + 1] : p0[2 * i + 1]), s, hi);
-                        acc2[(c * kLdCols) / 2 + i] = ts_pack_f32x2(__float_as_uint(lo), __float_as_uint(hi));
-#endif
                     }
                 }
                 ++it;

@@ -162,6 +162,14 @@ TS_DEV void ts_tma_store_2d_hint(const TsTensorMap* m, ts_u32 src, int c0, int c
         "cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3}], [%1], %4;"
         :: "l"((ts_u64)m), "r"(src), "r"(c0), "r"(c1), "l"(policy) : "memory");
 }
+// Shared memory -> global with an fp32 add at the destination (the tensor map's element type is fp32): the tile
+// is added into what the destination holds, element by element, in the memory system of the GPU that owns it.
+// A store-type operation: nothing is read back.  Concurrent adds to one element arrive in no fixed order.
+TS_DEV void ts_tma_reduce_add_2d(const TsTensorMap* m, ts_u32 src, int c0, int c1) {
+    asm volatile(
+        "cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+        :: "l"((ts_u64)m), "r"(src), "r"(c0), "r"(c1) : "memory");
+}
 TS_DEV void ts_bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N> TS_DEV void ts_bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" :: "n"(N) : "memory"); }
 TS_DEV void ts_bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }

@@ -174,6 +174,18 @@ int tesserae_launch_kernel_ex(void* function, const int grid[3], const int block
         attr[0].value.clusterDim.z = cluster[2];
         cfg.numAttrs = 1;
     }
+    // More than 48 KB of dynamic shared memory needs the function's opt-in; a caller that got the function from
+    // tesserae_get_function has no other way to give it.  (Plans set it once at creation.)
+    if (smem_bytes > 48 * 1024) {
+        static thread_local void* opted_fn = nullptr;
+        static thread_local int opted_bytes = 0;
+        if (opted_fn != function || opted_bytes < smem_bytes) {
+            CUresult arc = api->cuFuncSetAttribute(static_cast<CUfunction>(function),
+                                                   CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, smem_bytes);
+            if (arc != CUDA_SUCCESS) return fail(driver_error(api, "cuFuncSetAttribute(max dynamic smem)", arc));
+            opted_fn = function; opted_bytes = smem_bytes;
+        }
+    }
     CUresult rc = api->cuLaunchKernelEx(&cfg, static_cast<CUfunction>(function),
                                         params.empty() ? nullptr : params.data(), nullptr);
     if (rc != CUDA_SUCCESS) return fail(driver_error(api, "cuLaunchKernelEx", rc));

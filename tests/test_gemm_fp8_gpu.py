@@ -138,11 +138,10 @@ def test_needs_scales_and_k_multiple(torch_cuda):
         plan.run_scaled(x, x, c, s, s, None, 1.0, 256, 256, 192)
 
 
-@pytest.mark.parametrize("tuning", ["FP8_SPLIT=0", "FP8_PROMO_WARPS=16", "FP8_FMA2=0", "FP8_XPIPE=0"])
+@pytest.mark.parametrize("tuning", ["FP8_SPLIT=0", "FP8_PROMO_WARPS=16"])
 def test_structure_variants_agree(torch_cuda, tuning):
     """The kernel's structural variants (one 256-wide MMA chain instead of two 128-wide ones; sixteen promotion warps
-    instead of eight; scalar instead of packed-pair multiply-adds; each K block's first tensor-memory load after instead
-    of before the previous block's last multiply-adds) are other schedules of the same arithmetic: per K block the same fp32 partial product, scaled
+    instead of eight) are other schedules of the same arithmetic: per K block the same fp32 partial product, scaled
     and added in the same order.  Their outputs must equal the default build's bit for bit."""
     m, n, k = 640, 768, 1024
     p = O.make_fp8_problem(m, n, k, seed=260)

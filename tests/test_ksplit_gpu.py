@@ -167,3 +167,29 @@ def test_config5_full_size(torch_cuda, plan_f32):
     want_rowsum = (a.double() @ colsum).cpu().numpy()
     got_rowsum = total.sum(dim=1).cpu().numpy()
     assert np.max(np.abs(got_rowsum - want_rowsum)) <= 1e-3 * float(np.sqrt(np.mean(want_rowsum ** 2)))
+
+
+def test_scatter_add_epilogue_matches_plain_partial(torch_cuda, plan_f32):
+    """The adding form of the row-scattered epilogue (TMA reduce at the destination) with all owners on this GPU:
+    into zeroed buffers it must leave exactly the rows of the ordinary fp32 partial (0 + x = x), and a second launch
+    on top of the first exactly twice that (x + x is exact in fp32)."""
+    t = torch_cuda
+    m, n, k, owners = 1024 + 256, 768, 1024, 4
+    rpo = 384
+    p = O.make_bf16_problem(m, n, k, seed=72, scale=0.5)
+    a = t.from_numpy(p["a_bits"].view(np.int16)).view(t.bfloat16).cuda()
+    b = t.from_numpy(p["b_bits"].view(np.int16)).view(t.bfloat16).cuda()
+    s = t.cuda.current_stream().cuda_stream
+    plain = t.empty((m, n), dtype=t.float32, device="cuda")
+    plan_f32.ksplit_partials(a, b, plain, plain.numel() * 4, m, n, k, 1, stream=s)
+    radd = api.GemmPlan(api.KernelSpec(name="gemm_bf16_cg2_f32_scatter_add", elem=api.BF16, tile=(128, 256, 64),
+                                       cta_group=2, out_elem=api.F32, scatter=2))
+    dst = [t.zeros((rpo, n), dtype=t.float32, device="cuda") for _ in range(owners)]
+    for times in (1, 2):
+        radd.ksplit_scatter(a, b, [d.data_ptr() for d in dst], rpo, m, n, k, stream=s)
+        assert radd.status() == 0
+        for g in range(owners):
+            rows = min(rpo, m - g * rpo)
+            assert t.equal(dst[g][:rows], plain[g * rpo:g * rpo + rows] * times), (g, times)
+            assert (dst[g][rows:] == 0).all()              # nothing added past the owner's slice
+    radd.close()
