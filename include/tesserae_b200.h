@@ -238,10 +238,9 @@ typedef struct tesserae_kernel_spec {
                         1 = each tile is stored to the owner's slot, 2 = each tile is added into the owner's buffer */
     /* Optional overrides of the kernel's tuning choices, "NAME=VALUE;NAME=VALUE" (NULL or "" = the defaults).
      * The kernel a plan runs is a function of its spec alone; nothing is read from the environment.  Names:
-     *   GROUP_M=1..64          M-tiles per raster group of the persistent tile order
+     *   GROUP_M=1..64          M-tiles per raster group of the persistent tile order (default: sized per launch so
+     *                          that a group's panel of A, group_m x 128*cta_group rows x K, is about 32 MB)
      *   STORE_BUFS=2..4        dense kernel: staging buffers per epilogue warp
-     *   L2_HINT=0..7           dense kernel: L2 eviction hints, bit 1 = A tiles evict_last, 2 = B tiles evict_first,
-     *                          4 = stores of C evict_first
      *   FP8_PROMO_WARPS=8|16   block-scaled FP8: promotion warps
      *   FP8_SPLIT=0|1          block-scaled FP8: one MMA chain per tile width / per 128 columns
      * An unknown name or a value out of range fails with IncompatibleTile. */

@@ -142,7 +142,6 @@ int derive_config(const tesserae_kernel_spec& ks, KernelConfig* cfg, std::string
             const int v = kv.second;
             bool ok = true;
             if (key == "GROUP_M") { ok = v >= 1 && v <= 64; c.group_m = v; }
-            else if (key == "L2_HINT") { ok = v >= 0 && v <= 7; c.l2_hint = v; }
             else if (key == "STORE_BUFS") { ok = v >= 2 && v <= 4; c.store_bufs = v; }
             else if (key == "FP8_PROMO_WARPS") { ok = v == 8 || v == 16; want_promo_warps = v; }
             else if (key == "FP8_SPLIT") { ok = v == 0 || v == 1; c.fp8_split = v; }
@@ -264,8 +263,7 @@ BackendOutput emit(const KernelConfig& c) {
     if (c.scale_mode == TESSERAE_SCALE_FP8_BLOCK) {
         o.includes += std::string("#define TS_FP8_SPLIT ") + (c.fp8_split ? "1\n" : "0\n");
     }
-    o.includes += "#define TS_GROUP_M " + std::to_string(c.group_m) + "\n";
-    if (c.scale_mode == TESSERAE_SCALE_NONE) o.includes += "#define TS_L2_HINT " + std::to_string(c.l2_hint) + "\n";
+    o.includes += "// raster group height: " + (c.group_m > 0 ? std::to_string(c.group_m) + " M-tiles (from the spec)" : std::string("chosen per launch")) + "\n";
     o.helpers = strip_pragma_once(kSrcPtxSm100);
     const bool block_fp8 = c.scale_mode == TESSERAE_SCALE_FP8_BLOCK;
     const bool nvfp4 = c.scale_mode == TESSERAE_SCALE_NVFP4;
@@ -281,10 +279,10 @@ BackendOutput emit(const KernelConfig& c) {
              "// lib/backend/backend_cute.ml:368-429, cudaLaunchKernelEx with a cluster attribute):\n"
              "//   grid  = (%d * min(tiles, resident clusters), 1, 1)   tiles = ceil(M/%d) * ceil(N/%d)\n"
              "//   block = (%d, 1, 1)   cluster = (%d, 1, 1)   dynamic smem = %d\n"
-             "//   args  = A_tmap, B_tmap, C_tmap (CUtensorMap by value), %sbias, alpha, M, N, K, status\n"
+             "//   args  = A_tmap, B_tmap, C_tmap (CUtensorMap by value), %sbias, alpha, M, N, K, group_m, status\n"
              "//   tesserae_launch_kernel_ex(fn, grid, block, cluster, %d, stream, args, %d);\n",
              c.cta_group, c.block_m * c.cta_group, c.block_n, c.threads, c.cta_group, c.smem_bytes,
-             block_fp8 ? "scale_a, scale_b, " : nvfp4 ? "SFA_tmap, SFB_tmap, " : "", c.smem_bytes, (block_fp8 || nvfp4) ? 11 : 9);
+             block_fp8 ? "scale_a, scale_b, " : nvfp4 ? "SFA_tmap, SFB_tmap, " : "", c.smem_bytes, (block_fp8 || nvfp4) ? 12 : 10);
     o.host_launcher = buf;
     o.full_source = o.includes + o.helpers + "\n" + body + "\n" + o.host_launcher;
     return o;

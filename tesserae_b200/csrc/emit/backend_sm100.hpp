@@ -23,8 +23,7 @@ struct KernelConfig {
     int scatter = 0;         // row-scattered output (dense kernel only): 1 stored to per-source slots, 2 added into the owner's buffer
     int promo_warps = 0;     // promotion warps of the FP8 block-scaled kernel (0 elsewhere)
     int store_bufs = 2;      // dense kernel: staging buffers per epilogue warp (4 when the stores cross NVLink)
-    int group_m = 8;         // M-tiles per raster group of the persistent tile order
-    int l2_hint = 0;         // dense kernel: bit mask of L2 eviction hints (1 A evict_last, 2 B evict_first, 4 C stores evict_first)
+    int group_m = 0;         // M-tiles per raster group of the persistent tile order; 0 = sized per launch from M and K
     int fp8_split = 1;       // FP8 block-scaled: 1 = one MMA chain and TMEM buffer per 128 columns, 0 = per tile width
     int b_box_rows = 128;    // rows of B one TMA load brings (the FP8 block-scaled pair kernel loads B per 128-column MMA group)
     int threads = 192;

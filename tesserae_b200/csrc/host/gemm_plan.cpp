@@ -359,6 +359,25 @@ static int check_plan_device(const tesserae_gemm_plan* p, const char* what) {
     return 0;
 }
 
+// Height of the raster groups in M-tiles.  All tiles of a group read the group's panel of A (group_m M-tiles x K)
+// again for every N-tile while B streams through once per group, so the panel should stay resident in L2: it is sized
+// to about a quarter of the 126 MB L2 (the rest holds the B tiles in flight and the output on its way out).  Larger
+// groups re-read B fewer times: with 8-tile groups the NVFP4 case (1 MB of A per M-tile) fetched B eight times.
+// When K is so long that not even 8 M-tiles of A fit that budget, residency is out of reach and what is left is the
+// reuse between the tiles in flight together, which march through K in step: about 74 clusters = 8 M-tiles x 9 N-tiles
+// minimises the rows of A and B they touch, so the group height never goes below 8.
+static int pick_group_m(const KernelConfig& cfg, int64_t m, int64_t k) {
+    const int64_t tile_m = 128 * cfg.cta_group;
+    const int64_t num_m = (m + tile_m - 1) / tile_m;
+    if (cfg.group_m > 0) return int(cfg.group_m < num_m ? cfg.group_m : (num_m > 0 ? num_m : 1));
+    const int64_t panel = tile_m * (k * tesserae::spec::elem_bits(cfg.elem) / 8);     // bytes of A per M-tile
+    int64_t g = (int64_t(32) << 20) / (panel > 0 ? panel : 1);
+    if (g < 8) g = 8;
+    if (g > 64) g = 64;
+    if (g > num_m) g = num_m;
+    return int(g < 1 ? 1 : g);
+}
+
 // lda / ldb / ldc: row pitch in elements of A (M x K), B (N x K) and C (M x N); 0 = dense.
 static int gemm_launch(tesserae_gemm_plan* p, const void* a, int64_t lda, const void* b, int64_t ldb, void* c, int64_t ldc,
                        const tesserae_gemm_scales* scales, const void* bias,
@@ -411,7 +430,7 @@ static int gemm_launch(tesserae_gemm_plan* p, const void* a, int64_t lda, const 
     const int grid[3] = {clusters * cfg.cta_group, 1, 1};
     const int block[3] = {cfg.threads, 1, 1};
     const int cluster[3] = {cfg.cta_group, 1, 1};
-    const int mi = int(m), ni = int(n), ki = int(k);
+    const int mi = int(m), ni = int(n), ki = int(k), gmi = pick_group_m(cfg, m, k);
     if (cfg.scale_mode == TESSERAE_SCALE_NVFP4) {
         // Scale tables: [row blocks * K/64] chunks of 512 bytes, addressed as rows of 128 32-bit words;
         // one stage of one row block is 4 consecutive rows.
@@ -423,21 +442,21 @@ static int gemm_launch(tesserae_gemm_plan* p, const void* a, int64_t lda, const 
         const float alpha_eff = alpha * scales->global_a * scales->global_b;
         const tesserae_launch_arg args[] = {
             {tm_a, 128}, {tm_b, 128}, {tm_c, 128}, {tm_sfa, 128}, {tm_sfb, 128}, {&bias, sizeof(void*)},
-            {&alpha_eff, sizeof(float)}, {&mi, sizeof(int)}, {&ni, sizeof(int)}, {&ki, sizeof(int)},
+            {&alpha_eff, sizeof(float)}, {&mi, sizeof(int)}, {&ni, sizeof(int)}, {&ki, sizeof(int)}, {&gmi, sizeof(int)},
             {&p->d_status, sizeof(void*)}};
-        return tesserae_launch_kernel_ex(p->function, grid, block, cluster, cfg.smem_bytes, stream, args, 11);
+        return tesserae_launch_kernel_ex(p->function, grid, block, cluster, cfg.smem_bytes, stream, args, 12);
     }
     if (cfg.scale_mode == TESSERAE_SCALE_FP8_BLOCK) {
         const tesserae_launch_arg args[] = {
             {tm_a, 128}, {tm_b, 128}, {tm_c, 128}, {&scales->scale_a, sizeof(void*)}, {&scales->scale_b, sizeof(void*)},
             {&bias, sizeof(void*)}, {&alpha, sizeof(float)}, {&mi, sizeof(int)}, {&ni, sizeof(int)}, {&ki, sizeof(int)},
-            {&p->d_status, sizeof(void*)}};
-        return tesserae_launch_kernel_ex(p->function, grid, block, cluster, cfg.smem_bytes, stream, args, 11);
+            {&gmi, sizeof(int)}, {&p->d_status, sizeof(void*)}};
+        return tesserae_launch_kernel_ex(p->function, grid, block, cluster, cfg.smem_bytes, stream, args, 12);
     }
     const tesserae_launch_arg args[] = {
         {tm_a, 128}, {tm_b, 128}, {tm_c, 128}, {&bias, sizeof(void*)}, {&alpha, sizeof(float)},
-        {&mi, sizeof(int)}, {&ni, sizeof(int)}, {&ki, sizeof(int)}, {&p->d_status, sizeof(void*)}};
-    return tesserae_launch_kernel_ex(p->function, grid, block, cluster, cfg.smem_bytes, stream, args, 9);
+        {&mi, sizeof(int)}, {&ni, sizeof(int)}, {&ki, sizeof(int)}, {&gmi, sizeof(int)}, {&p->d_status, sizeof(void*)}};
+    return tesserae_launch_kernel_ex(p->function, grid, block, cluster, cfg.smem_bytes, stream, args, 10);
 }
 
 int tesserae_gemm_run_scaled(tesserae_gemm_plan* p, const void* a, const void* b, void* c,
@@ -514,13 +533,13 @@ int tesserae_gemm_ksplit_scatter(tesserae_gemm_plan* p, const void* a, const voi
     const int grid[3] = {clusters * cfg.cta_group, 1, 1};
     const int block[3] = {cfg.threads, 1, 1};
     const int cluster[3] = {cfg.cta_group, 1, 1};
-    const int mi = int(m), ni = int(n), ki = int(k), rpo = int(rows_per_owner);
+    const int mi = int(m), ni = int(n), ki = int(k), rpo = int(rows_per_owner), gmi = pick_group_m(cfg, m, k);
     const void* no_bias = nullptr;
     const float one = 1.0f;
     const tesserae_launch_arg args[] = {
         {tm_a, 128}, {tm_b, 128}, {&tm_c, sizeof tm_c}, {&rpo, sizeof(int)}, {&no_bias, sizeof(void*)}, {&one, sizeof(float)},
-        {&mi, sizeof(int)}, {&ni, sizeof(int)}, {&ki, sizeof(int)}, {&p->d_status, sizeof(void*)}};
-    return tesserae_launch_kernel_ex(p->function, grid, block, cluster, cfg.smem_bytes, stream, args, 10);
+        {&mi, sizeof(int)}, {&ni, sizeof(int)}, {&ki, sizeof(int)}, {&gmi, sizeof(int)}, {&p->d_status, sizeof(void*)}};
+    return tesserae_launch_kernel_ex(p->function, grid, block, cluster, cfg.smem_bytes, stream, args, 11);
 }
 
 int tesserae_gemm_ksplit_run(tesserae_gemm_plan* p, const void* a, const void* b, void* c_bf16, void* scratch,

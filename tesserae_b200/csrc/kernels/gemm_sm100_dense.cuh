@@ -30,10 +30,6 @@
 //   TS_AB_FMT        operand format code of the instruction descriptor
 //   TS_OUT_F32       0: bf16 output, 1: fp32 output
 //   TS_HAS_BIAS      0/1: add bias[n] (bf16) after alpha scaling
-//   TS_GROUP_M       M-tiles per raster group (L2 reuse)
-//   TS_L2_HINT       bit mask of L2 eviction hints: 1 = A tiles evict_last (the raster group's A panel is read again
-//                    by every wave of the group), 2 = B tiles evict_first (a B tile is used by one wave), 4 = the
-//                    stores of C evict_first
 //   TS_SCATTER       0/1: row-scattered output.  Rows [g*rows_per_owner, (g+1)*rows_per_owner) of C are
 //                    stored through tensor map g of an array of up to 8 (one per owner), at row
 //                    (row - g*rows_per_owner).  With maps that point into the owners' memory this is the
@@ -54,14 +50,8 @@
 struct TsTensorMapArray8 { TsTensorMap m[8]; };
 #endif
 
-#ifndef TS_GROUP_M
-#define TS_GROUP_M 8
-#endif
 #ifndef TS_SWIZZLE_B
 #define TS_SWIZZLE_B 3
-#endif
-#ifndef TS_L2_HINT
-#define TS_L2_HINT 0
 #endif
 
 namespace ts_dense {
@@ -100,16 +90,6 @@ static_assert(kBlockN % kChunkCols == 0, "TS_BLOCK_N must be a multiple of the s
 static_assert(kNumAcc * kBlockN <= 512, "accumulators exceed tensor memory");
 static_assert(kSmemTotal + 1024 <= 232448, "shared memory over the 227 KB limit");
 
-TS_DEV void decode_tile(ts_u32 t, ts_u32 num_m, ts_u32 num_n, ts_u32& m_blk, ts_u32& n_blk) {
-    const ts_u32 group_size = TS_GROUP_M * num_n;
-    const ts_u32 g = t / group_size;
-    const ts_u32 first_m = g * TS_GROUP_M;
-    const ts_u32 gm = (num_m - first_m < TS_GROUP_M) ? (num_m - first_m) : TS_GROUP_M;
-    const ts_u32 r = t - g * group_size;
-    m_blk = first_m + r % gm;
-    n_blk = r / gm;
-}
-
 }  // namespace ts_dense
 
 extern "C" __global__ void __launch_bounds__(192, 1)
@@ -121,7 +101,7 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
                const __grid_constant__ TsTensorMap tmap_c,
 #endif
                const ts_u16* __restrict__ bias,
-               float alpha, int M, int N, int K,
+               float alpha, int M, int N, int K, int group_m,
                ts_u32* __restrict__ status)
 {
     using namespace ts_dense;
@@ -185,12 +165,9 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
             // In a pair, every byte count is signalled on the leader CTA's full barrier.
             ts_u32 it = 0;
             bool ok = true;
-#if TS_L2_HINT & 3
-            const ts_u64 pol_last = ts_l2_policy_evict_last(), pol_first = ts_l2_policy_evict_first();
-#endif
             for (ts_u32 t = first_tile; t < num_tiles && ok; t += tile_step) {
                 ts_u32 m_blk, n_blk;
-                decode_tile(t, num_m, num_n, m_blk, n_blk);
+                ts_decode_tile(t, num_m, num_n, (ts_u32)group_m, m_blk, n_blk);
                 const int a_row = (int)(m_blk * kTileM + cta_rank * kBlockM);
                 const int b_row = (int)(n_blk * kBlockN + cta_rank * kLoadN);
                 for (ts_u32 kb = 0; kb < num_k_blocks; ++kb, ++it) {
@@ -202,29 +179,13 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
                     const int kc = (int)(kb * kBlockK);
                     if (TS_CTA_GROUP == 1) {
                         ts_mbar_arrive_expect_tx(full_bar + 8 * s, kStageBytes);
-#if TS_L2_HINT & 1
-                        ts_tma_load_2d_hint(smem_a + s * kSmemA, &tmap_a, full_bar + 8 * s, kc, a_row, pol_last);
-#else
                         ts_tma_load_2d(smem_a + s * kSmemA, &tmap_a, full_bar + 8 * s, kc, a_row);
-#endif
-#if TS_L2_HINT & 2
-                        ts_tma_load_2d_hint(smem_b + s * kSmemB, &tmap_b, full_bar + 8 * s, kc, b_row, pol_first);
-#else
                         ts_tma_load_2d(smem_b + s * kSmemB, &tmap_b, full_bar + 8 * s, kc, b_row);
-#endif
                     } else {
                         const ts_u32 leader_full = ts_mapa(full_bar + 8 * s, 0);
                         if (is_leader) ts_mbar_arrive_expect_tx(full_bar + 8 * s, kStageBytes * 2);
-#if TS_L2_HINT & 1
-                        ts_tma_load_2d_pair_hint(smem_a + s * kSmemA, &tmap_a, leader_full, kc, a_row, pol_last);
-#else
                         ts_tma_load_2d_pair(smem_a + s * kSmemA, &tmap_a, leader_full, kc, a_row);
-#endif
-#if TS_L2_HINT & 2
-                        ts_tma_load_2d_pair_hint(smem_b + s * kSmemB, &tmap_b, leader_full, kc, b_row, pol_first);
-#else
                         ts_tma_load_2d_pair(smem_b + s * kSmemB, &tmap_b, leader_full, kc, b_row);
-#endif
                     }
                 }
             }
@@ -287,12 +248,9 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
         const ts_u32 leader_tmem_empty = (TS_CTA_GROUP == 2) ? ts_mapa(tmem_empty_bar, 0) : tmem_empty_bar;
         ts_u32 tile_iter = 0, chunk_iter = 0;
         bool ok = true;
-#if TS_L2_HINT & 4
-        const ts_u64 pol_store = ts_l2_policy_evict_first();
-#endif
         for (ts_u32 t = first_tile; t < num_tiles && ok; t += tile_step, ++tile_iter) {
             ts_u32 m_blk, n_blk;
-            decode_tile(t, num_m, num_n, m_blk, n_blk);
+            ts_decode_tile(t, num_m, num_n, (ts_u32)group_m, m_blk, n_blk);
             const ts_u32 acc = tile_iter % kNumAcc;
             const ts_u32 acc_ph = (tile_iter / kNumAcc) & 1u;
             if (!ts_mbar_wait(tmem_full_bar + 8 * acc, acc_ph)) {
@@ -367,11 +325,7 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
 #endif
                     }
 #else
-#if TS_L2_HINT & 4
-                    if (col0 < (ts_u32)N && row0 < M) ts_tma_store_2d_hint(&tmap_c, buf, (int)col0, row0, pol_store);
-#else
                     if (col0 < (ts_u32)N && row0 < M) ts_tma_store_2d(&tmap_c, buf, (int)col0, row0);
-#endif
 #endif
                     ts_bulk_commit();   // committed even when empty so that "one group pending" always means the previous chunk
                 }

@@ -28,12 +28,9 @@
 //    has landed; the epilogue fills all staging buffers of the warp before one fence and commit.
 //
 // Compile-time configuration (macros): TS_KERNEL_NAME, TS_CTA_GROUP (1|2), TS_BLOCK_N (128|256),
-// TS_STAGES, TS_PROMO_WARPS (8|16), TS_OUT_F32, TS_HAS_BIAS, TS_GROUP_M, TS_FP8_SPLIT.
+// TS_STAGES, TS_PROMO_WARPS (8|16), TS_OUT_F32, TS_HAS_BIAS, TS_FP8_SPLIT.
 #pragma once
 
-#ifndef TS_GROUP_M
-#define TS_GROUP_M 8
-#endif
 #ifndef TS_PROMO_WARPS
 #define TS_PROMO_WARPS 8
 #endif
@@ -90,35 +87,6 @@ static_assert(kSmemTotal + 1024 <= 232448, "shared memory over the 227 KB limit"
 TS_DEV void ts_tmem_ld(ts_u32 taddr, ts_u32 (&r)[16]) { ts_tmem_ld_32x32b_x16(taddr, r); }
 TS_DEV void ts_tmem_ld(ts_u32 taddr, ts_u32 (&r)[32]) { ts_tmem_ld_32x32b_x32(taddr, r); }
 
-TS_DEV void decode_tile(ts_u32 t, ts_u32 num_m, ts_u32 num_n, ts_u32& m_blk, ts_u32& n_blk) {
-    const ts_u32 group_size = TS_GROUP_M * num_n;
-    const ts_u32 g = t / group_size;
-    const ts_u32 first_m = g * TS_GROUP_M;
-    const ts_u32 gm = (num_m - first_m < TS_GROUP_M) ? (num_m - first_m) : TS_GROUP_M;
-    const ts_u32 r = t - g * group_size;
-    m_blk = first_m + r % gm;
-    n_blk = r / gm;
-}
-// The same map without a run-time integer division on the common path (the promotion warps decode between two
-// tiles, where three dependent divisions were a visible part of the gap): t / group_size by a float reciprocal with
-// an exact correction (t < 2^22), the split inside a full group by the compile-time group height.
-TS_DEV void decode_tile_fast(ts_u32 t, ts_u32 num_m, ts_u32 num_n, float inv_group, ts_u32& m_blk, ts_u32& n_blk) {
-    const ts_u32 group_size = TS_GROUP_M * num_n;
-    ts_u32 g = (ts_u32)__float2uint_rz(__uint2float_rz(t) * inv_group);
-    int r = (int)t - (int)(g * group_size);
-    if (r < 0) { g -= 1u; r += (int)group_size; }
-    else if (r >= (int)group_size) { g += 1u; r -= (int)group_size; }
-    const ts_u32 first_m = g * TS_GROUP_M;
-    if (num_m - first_m >= TS_GROUP_M) {
-        m_blk = first_m + (ts_u32)r % TS_GROUP_M;
-        n_blk = (ts_u32)r / TS_GROUP_M;
-    } else {
-        const ts_u32 gm = num_m - first_m;
-        m_blk = first_m + (ts_u32)r % gm;
-        n_blk = (ts_u32)r / gm;
-    }
-}
-
 }  // namespace ts_fp8
 
 extern "C" __global__ void __launch_bounds__(128 + 32 * TS_PROMO_WARPS, 1)
@@ -128,7 +96,7 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
                const float* __restrict__ scale_a,      // [M][K/128]
                const float* __restrict__ scale_b,      // [ceil(N/128)][K/128]
                const ts_u16* __restrict__ bias,
-               float alpha, int M, int N, int K,
+               float alpha, int M, int N, int K, int group_m,
                ts_u32* __restrict__ status)
 {
     using namespace ts_fp8;
@@ -193,7 +161,7 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
             bool ok = true;
             for (ts_u32 t = first_tile; t < num_tiles && ok; t += tile_step) {
                 ts_u32 m_blk, n_blk;
-                decode_tile(t, num_m, num_n, m_blk, n_blk);
+                ts_decode_tile(t, num_m, num_n, (ts_u32)group_m, m_blk, n_blk);
                 const int a_row = (int)(m_blk * kTileM + cta_rank * kBlockM);
                 const int b_row = (int)(n_blk * kBlockN + cta_rank * kLoadN);
                 for (ts_u32 kb = 0; kb < num_k_blocks; ++kb, ++it) {
@@ -316,17 +284,17 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
         // tile they run behind the first wait, at its end they would sit in front of the next tile's first load).
         ts_u32 m_blk = 0, n_blk = 0;
         const bool fast_decode = num_tiles < (1u << 22);
-        const float inv_group = 1.0f / (float)(TS_GROUP_M * num_n);
+        const float inv_group = 1.0f / (float)((ts_u32)group_m * num_n), inv_gm = 1.0f / (float)group_m;
         if (first_tile < num_tiles) {
-            decode_tile(first_tile, num_m, num_n, m_blk, n_blk);
+            ts_decode_tile(first_tile, num_m, num_n, (ts_u32)group_m, m_blk, n_blk);
             scales_of_tile(m_blk, n_blk);
         }
         for (ts_u32 t = first_tile; t < num_tiles && ok; t += tile_step) {
             const bool has_next = t + tile_step < num_tiles;
             ts_u32 m_next = 0, n_next = 0;
             if (has_next) {
-                if (fast_decode) decode_tile_fast(t + tile_step, num_m, num_n, inv_group, m_next, n_next);
-                else             decode_tile(t + tile_step, num_m, num_n, m_next, n_next);
+                if (fast_decode) ts_decode_tile_fast(t + tile_step, num_m, num_n, (ts_u32)group_m, inv_group, inv_gm, m_next, n_next);
+                else             ts_decode_tile(t + tile_step, num_m, num_n, (ts_u32)group_m, m_next, n_next);
             }
             const ts_u32 col_base = n_blk * kBlockN + half * kWarpCols;
             // 128 x BLOCK_N fp32 accumulators of the tile, one row per lane, held as packed pairs: the multiply-adds

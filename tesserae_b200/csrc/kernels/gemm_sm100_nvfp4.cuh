@@ -29,12 +29,9 @@
 // hands it back to the MMA issuer as soon as the second pass is in registers.
 //
 // Compile-time configuration (macros): TS_KERNEL_NAME, TS_CTA_GROUP (1|2), TS_BLOCK_N (128|256),
-// TS_STAGES, TS_OUT_F32, TS_HAS_BIAS, TS_GROUP_M.
+// TS_STAGES, TS_OUT_F32, TS_HAS_BIAS.
 #pragma once
 
-#ifndef TS_GROUP_M
-#define TS_GROUP_M 8
-#endif
 
 namespace ts_nvfp4 {
 
@@ -79,16 +76,6 @@ static_assert(kWarpCols % kPassCols == 0 && kPassCols % kChunkCols == 0, "bad ep
 static_assert(kSfaCols == 16 && (kSfbCols == 16 || kSfbCols == 32), "scale stores are written for 16-column groups");
 static_assert(kSmemTotal + 1024 <= 232448, "shared memory over the 227 KB limit");
 
-TS_DEV void decode_tile(ts_u32 t, ts_u32 num_m, ts_u32 num_n, ts_u32& m_blk, ts_u32& n_blk) {
-    const ts_u32 group_size = TS_GROUP_M * num_n;
-    const ts_u32 g = t / group_size;
-    const ts_u32 first_m = g * TS_GROUP_M;
-    const ts_u32 gm = (num_m - first_m < TS_GROUP_M) ? (num_m - first_m) : TS_GROUP_M;
-    const ts_u32 r = t - g * group_size;
-    m_blk = first_m + r % gm;
-    n_blk = r / gm;
-}
-
 }  // namespace ts_nvfp4
 
 extern "C" __global__ void __launch_bounds__(448, 1)
@@ -98,7 +85,7 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
                const __grid_constant__ TsTensorMap tmap_sfa,   // u32 [row blocks * K groups][128], box {128, 4}
                const __grid_constant__ TsTensorMap tmap_sfb,
                const ts_u16* __restrict__ bias,
-               float alpha, int M, int N, int K,
+               float alpha, int M, int N, int K, int group_m,
                ts_u32* __restrict__ status)
 {
     using namespace ts_nvfp4;
@@ -169,7 +156,7 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
             bool ok = true;
             for (ts_u32 t = first_tile; t < num_tiles && ok; t += tile_step) {
                 ts_u32 m_blk, n_blk;
-                decode_tile(t, num_m, num_n, m_blk, n_blk);
+                ts_decode_tile(t, num_m, num_n, (ts_u32)group_m, m_blk, n_blk);
                 const int a_row = (int)(m_blk * kTileM + cta_rank * kBlockM);
                 const int b_row = (int)(n_blk * kBlockN + cta_rank * kLoadN);
                 const ts_u32 sfa_rb = m_blk * TS_CTA_GROUP + cta_rank;      // this CTA's 128-row block of A
@@ -180,6 +167,17 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
                     if (!ts_mbar_wait(empty_bar + 8 * s, ph ^ 1u)) {
                         atomicOr(status, TS_ERR_TIMEOUT_EMPTY); ok = false; break;
                     }
+                    // Scales first: they have one more hop to make than the operands (shared memory -> registers ->
+                    // tensor memory, by the scale warps) before the MMAs of the stage can start.
+                    // scales: 4 chunks (rows of the chunk table) per 128-row block and stage, into this CTA's
+                    // own shared memory and onto its own barrier; each CTA of a pair fetches all of the B tile's
+                    const ts_u32 sbar = sf_full_bar + 8 * s;
+                    ts_mbar_arrive_expect_tx(sbar, kScaleBytes);
+                    ts_tma_load_2d(smem_sfa + s * kSmemSfa, &tmap_sfa, sbar, 0, (int)(sfa_rb * k_groups + kb * 4));
+#pragma unroll
+                    for (ts_u32 nb = 0; nb < kNBlocks; ++nb)
+                        ts_tma_load_2d(smem_sfb + s * kSmemSfb + nb * kNumUmma * kSfChunk, &tmap_sfb, sbar, 0,
+                                       (int)((sfb_rb + nb) * k_groups + kb * 4));
                     const int kc = (int)(kb * 128u);                         // byte column of this stage in A and B
                     if (TS_CTA_GROUP == 1) {
                         ts_mbar_arrive_expect_tx(full_bar + 8 * s, kOperandBytes);
@@ -191,15 +189,6 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
                         ts_tma_load_2d_pair(smem_a + s * kSmemA, &tmap_a, leader_full, kc, a_row);
                         ts_tma_load_2d_pair(smem_b + s * kSmemB, &tmap_b, leader_full, kc, b_row);
                     }
-                    // scales: 4 chunks (rows of the chunk table) per 128-row block and stage, into this CTA's
-                    // own shared memory and onto its own barrier; each CTA of a pair fetches all of the B tile's
-                    const ts_u32 sbar = sf_full_bar + 8 * s;
-                    ts_mbar_arrive_expect_tx(sbar, kScaleBytes);
-                    ts_tma_load_2d(smem_sfa + s * kSmemSfa, &tmap_sfa, sbar, 0, (int)(sfa_rb * k_groups + kb * 4));
-#pragma unroll
-                    for (ts_u32 nb = 0; nb < kNBlocks; ++nb)
-                        ts_tma_load_2d(smem_sfb + s * kSmemSfb + nb * kNumUmma * kSfChunk, &tmap_sfb, sbar, 0,
-                                       (int)((sfb_rb + nb) * k_groups + kb * 4));
                 }
             }
         }
@@ -304,7 +293,7 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
         bool ok = true;
         for (ts_u32 t = first_tile; t < num_tiles && ok; t += tile_step, ++tile_iter) {
             ts_u32 m_blk, n_blk;
-            decode_tile(t, num_m, num_n, m_blk, n_blk);
+            ts_decode_tile(t, num_m, num_n, (ts_u32)group_m, m_blk, n_blk);
             const ts_u32 acc = tile_iter % kNumAcc;
             const ts_u32 acc_ph = (tile_iter / kNumAcc) & 1u;
             if (!ts_mbar_wait(tmem_full_bar + 8 * acc, acc_ph)) {
@@ -315,6 +304,66 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
             const ts_u32 t_row = tmem_base + ((quarter * 32u) << 16) + acc * kBlockN + half * kWarpCols;
             const int row0 = (int)(m_blk * kTileM + cta_rank * kBlockM + quarter * 32);
             const ts_u32 col_base = n_blk * kBlockN + half * kWarpCols;
+#if !TS_OUT_F32
+            if (kPasses == 2) {
+                // bf16 output, 128 columns per warp: the first 64 columns are scaled, biased and packed to bf16 in
+                // registers (32 words) at once, so that the second 64 can be loaded straight after them and the
+                // accumulator handed back to the MMA issuer before anything is staged or stored.  The time from
+                // "accumulator complete" to "accumulator free" is two TMEM loads and 64 conversions; it is the part
+                // of a tile that no MMA can overlap, because tensor memory has room for one 256-column accumulator.
+                ts_u32 v[kPassCols], w0[kPassCols / 2];
+                ts_tmem_ld_32x32b_x32(t_row, reinterpret_cast<ts_u32(&)[32]>(v[0]));
+                ts_tmem_ld_32x32b_x32(t_row + 32, reinterpret_cast<ts_u32(&)[32]>(v[32]));
+                ts_tmem_wait_ld();
+                auto pack8 = [&](ts_u32 col0, ts_u32 c, ts_u32 (&out)[4]) __attribute__((always_inline)) {
+                    float f[8];
+#pragma unroll
+                    for (ts_u32 i = 0; i < 8; ++i) f[i] = alpha * __uint_as_float(v[8 * c + i]);
+#if TS_HAS_BIAS
+                    if (col0 + 8 * c < (ts_u32)N) {
+                        const uint4 bb = __ldg(reinterpret_cast<const uint4*>(bias + col0 + 8 * c));
+                        f[0] += ts_bf16_lo_to_f32(bb.x); f[1] += ts_bf16_hi_to_f32(bb.x);
+                        f[2] += ts_bf16_lo_to_f32(bb.y); f[3] += ts_bf16_hi_to_f32(bb.y);
+                        f[4] += ts_bf16_lo_to_f32(bb.z); f[5] += ts_bf16_hi_to_f32(bb.z);
+                        f[6] += ts_bf16_lo_to_f32(bb.w); f[7] += ts_bf16_hi_to_f32(bb.w);
+                    }
+#endif
+                    out[0] = ts_pack_bf16x2(f[0], f[1]); out[1] = ts_pack_bf16x2(f[2], f[3]);
+                    out[2] = ts_pack_bf16x2(f[4], f[5]); out[3] = ts_pack_bf16x2(f[6], f[7]);
+                };
+#pragma unroll
+                for (ts_u32 c = 0; c < 8; ++c) pack8(col_base, c, reinterpret_cast<ts_u32(&)[4]>(w0[4 * c]));
+                ts_tmem_ld_32x32b_x32(t_row + kPassCols, reinterpret_cast<ts_u32(&)[32]>(v[0]));
+                ts_tmem_ld_32x32b_x32(t_row + kPassCols + 32, reinterpret_cast<ts_u32(&)[32]>(v[32]));
+                ts_tmem_wait_ld();
+                ts_tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    if (TS_CTA_GROUP == 2) ts_mbar_arrive_cluster(leader_tmem_empty + 8 * acc);
+                    else                   ts_mbar_arrive(tmem_empty_bar + 8 * acc);
+                }
+#pragma unroll
+                for (ts_u32 p = 0; p < 2; ++p) {
+                    const ts_u32 col0 = col_base + p * kPassCols;
+                    if (lane == 0) ts_bulk_wait_read<0>();         // the previous store has read the staging buffer
+                    __syncwarp();
+#pragma unroll
+                    for (ts_u32 c = 0; c < 8; ++c) {
+                        ts_u32 o[4];
+                        if (p == 0) { o[0] = w0[4 * c]; o[1] = w0[4 * c + 1]; o[2] = w0[4 * c + 2]; o[3] = w0[4 * c + 3]; }
+                        else pack8(col0, c, o);
+                        ts_st_shared_v4(row_addr + ((c << 4) ^ row_sw), o[0], o[1], o[2], o[3]);
+                    }
+                    ts_fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (col0 < (ts_u32)N && row0 < M) ts_tma_store_2d(&tmap_c, store_smem, (int)col0, row0);
+                        ts_bulk_commit();
+                    }
+                }
+                continue;
+            }
+#endif
 #pragma unroll
             for (ts_u32 p = 0; p < kPasses; ++p) {
                 ts_u32 v[kPassCols];

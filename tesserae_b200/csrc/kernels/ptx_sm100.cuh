@@ -137,31 +137,6 @@ TS_DEV void ts_tma_store_2d(const TsTensorMap* m, ts_u32 src, int c0, int c1) {
         "cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
         :: "l"((ts_u64)m), "r"(src), "r"(c0), "r"(c1) : "memory");
 }
-// The same copies with an L2 eviction-priority hint (a 64-bit policy made by createpolicy): operand panels
-// that later tiles read again are kept (evict_last), data that is used once passes through (evict_first).
-TS_DEV ts_u64 ts_l2_policy_evict_last() {
-    ts_u64 p; asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p)); return p;
-}
-TS_DEV ts_u64 ts_l2_policy_evict_first() {
-    ts_u64 p; asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p)); return p;
-}
-TS_DEV void ts_tma_load_2d_hint(ts_u32 dst, const TsTensorMap* m, ts_u32 bar, int c0, int c1, ts_u64 policy) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
-        " [%0], [%1, {%3, %4}], [%2], %5;"
-        :: "r"(dst), "l"((ts_u64)m), "r"(bar), "r"(c0), "r"(c1), "l"(policy) : "memory");
-}
-TS_DEV void ts_tma_load_2d_pair_hint(ts_u32 dst, const TsTensorMap* m, ts_u32 cluster_bar, int c0, int c1, ts_u64 policy) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
-        " [%0], [%1, {%3, %4}], [%2], %5;"
-        :: "r"(dst), "l"((ts_u64)m), "r"(cluster_bar), "r"(c0), "r"(c1), "l"(policy) : "memory");
-}
-TS_DEV void ts_tma_store_2d_hint(const TsTensorMap* m, ts_u32 src, int c0, int c1, ts_u64 policy) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3}], [%1], %4;"
-        :: "l"((ts_u64)m), "r"(src), "r"(c0), "r"(c1), "l"(policy) : "memory");
-}
 // Shared memory -> global with an fp32 add at the destination (the tensor map's element type is fp32): the tile
 // is added into what the destination holds, element by element, in the memory system of the GPU that owns it.
 // A store-type operation: nothing is read back.  Concurrent adds to one element arrive in no fixed order.
@@ -350,6 +325,44 @@ TS_DEV void ts_tmem_st_32x32b_x16(ts_u32 taddr, const ts_u32 (&r)[16]) {
 TS_DEV void ts_tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 TS_DEV void ts_ld_shared_v4(ts_u32 addr, ts_u32& a, ts_u32& b, ts_u32& c, ts_u32& d) {
     asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "r"(addr) : "memory");
+}
+
+// ---------------------------------------------------------------- tile order of the persistent kernels
+// Tiles are walked in raster groups of `group_m` M-tiles: inside a group the M index runs fastest, so the tiles
+// that are in flight together share a panel of A (group_m M-tiles) and a few N-tiles of B.  `group_m` is a launch
+// argument: the host sizes it so that the A panel of a group stays in L2 while the group sweeps all of B.
+TS_DEV void ts_decode_tile(ts_u32 t, ts_u32 num_m, ts_u32 num_n, ts_u32 group_m, ts_u32& m_blk, ts_u32& n_blk) {
+    const ts_u32 group_size = group_m * num_n;
+    const ts_u32 g = t / group_size;
+    const ts_u32 first_m = g * group_m;
+    const ts_u32 gm = (num_m - first_m < group_m) ? (num_m - first_m) : group_m;
+    const ts_u32 r = t - g * group_size;
+    m_blk = first_m + r % gm;
+    n_blk = r / gm;
+}
+// x / d through a float reciprocal with an exact correction; x < 2^22, d >= 1.
+TS_DEV ts_u32 ts_div_by_reciprocal(ts_u32 x, ts_u32 d, float inv_d) {
+    ts_u32 q = (ts_u32)__float2uint_rz(__uint2float_rz(x) * inv_d);
+    const int r = (int)x - (int)(q * d);
+    if (r < 0) q -= 1u; else if (r >= (int)d) q += 1u;
+    return q;
+}
+// The same map without an integer division on the common path (t < 2^22): for warps that decode between two tiles,
+// where dependent divisions are a visible part of the gap.  inv_group = 1 / (group_m * num_n), inv_gm = 1 / group_m.
+TS_DEV void ts_decode_tile_fast(ts_u32 t, ts_u32 num_m, ts_u32 num_n, ts_u32 group_m, float inv_group, float inv_gm,
+                                ts_u32& m_blk, ts_u32& n_blk) {
+    const ts_u32 group_size = group_m * num_n;
+    const ts_u32 g = ts_div_by_reciprocal(t, group_size, inv_group);
+    const ts_u32 r = t - g * group_size;
+    const ts_u32 first_m = g * group_m;
+    if (num_m - first_m >= group_m) {
+        n_blk = ts_div_by_reciprocal(r, group_m, inv_gm);
+        m_blk = first_m + r - n_blk * group_m;
+    } else {
+        const ts_u32 gm = num_m - first_m;
+        m_blk = first_m + r % gm;
+        n_blk = r / gm;
+    }
 }
 
 // ---------------------------------------------------------------- small utilities

@@ -69,8 +69,8 @@ def test_tuning_is_part_of_the_spec():
     base = api.KernelSpec(name="t0", elem=api.BF16, tile=(128, 256, 64))
     tuned = api.KernelSpec(name="t0", elem=api.BF16, tile=(128, 256, 64), tuning="GROUP_M=16; STORE_BUFS=3")
     a, b = api.backend_emit(base).includes, api.backend_emit(tuned).includes
-    assert "#define TS_GROUP_M 8" in a and "#define TS_STORE_BUFS 2" in a
-    assert "#define TS_GROUP_M 16" in b and "#define TS_STORE_BUFS 3" in b
+    assert "raster group height: chosen per launch" in a and "#define TS_STORE_BUFS 2" in a
+    assert "raster group height: 16 M-tiles" in b and "#define TS_STORE_BUFS 3" in b
     with pytest.raises(api.TesseraeError, match="unknown tuning name 'NOPE'"):
         api.backend_emit(api.KernelSpec(name="t1", tuning="NOPE=1"))
     with pytest.raises(api.TesseraeError, match="out of range: GROUP_M=0"):
