@@ -330,7 +330,7 @@ class Workload:
                 dst = [hdl.buffer_ptrs[g] + (buf * self.world + self.rank) * slot for g in range(self.world)]
                 if ev:
                     ev[0].record()
-                self.plan.ksplit_scatter(self.a, self.b, dst, rows, self.m, self.n, self.k, stream=self.stream)
+                self.plan.ksplit_scatter(self.a, self.b, dst, rows, self.m, self.n, self.k, stream=self.stream, start_owner=self.rank)
                 if ev:
                     ev[1].record()
                 hdl.barrier(channel=0)
@@ -362,15 +362,14 @@ class Workload:
                 dst = [hdl.buffer_ptrs[g] + buf * half for g in range(self.world)]
                 if ev:
                     ev[0].record()
-                self.plan.ksplit_scatter(self.a, self.b, dst, rows, self.m, self.n, self.k, stream=self.stream)
+                self.plan.ksplit_scatter(self.a, self.b, dst, rows, self.m, self.n, self.k, stream=self.stream, start_owner=self.rank)
                 if ev:
                     ev[1].record()
                 hdl.barrier(channel=0)
-                api.reduce_cast_bf16(acc[buf], 1, 0, self.c, rows * self.n, stream=self.stream)
-                acc[buf].zero_()
+                api.cast_clear_bf16(acc[buf], self.c, rows * self.n, stream=self.stream)
                 if ev:
                     ev[2].record()
-            self.launches_per_step = 3
+            self.launches_per_step = 2
             self.step = step
             self._finish_ksplit()
             return

@@ -298,6 +298,32 @@ typedef struct tesserae_backend_output {
 int tesserae_backend_emit(const tesserae_kernel_spec* spec, tesserae_backend_output* out);
 void tesserae_backend_output_free(tesserae_backend_output* out);
 
+/* ------------------------------------------------------------------ Tirix: the IR between descriptor and source
+ * The reference's second emission path goes descriptor -> Tirix IR -> source (lib/tirix/desc_to_tirix.ml:466-508,
+ * lib/tirix/tirix_emit.ml:481-501) with a scope / structure verifier in between (lib/tirix/tirix_verify.ml:9-183).
+ * Here the IR states, role by role, the structure of the sm_100a mainloop a spec selects, in the reference's
+ * statement forms (let / assign / op / if / for / pipeline / warpgroup / pragma / seq) and operations, extended by
+ * what the working kernels need (bounded waits only, TMA stores and reduce-adds, TMEM stores, the fp32 promotion).
+ * It has a line-oriented text form that prints and parses back, so a host can inspect or edit it as text.
+ * Emission goes through the IR: the program must verify and must have the structure of the mainloop its `origin`
+ * line selects; the emitted source carries the program's listing in its header. */
+typedef struct tesserae_tirix tesserae_tirix;
+/* Desc_to_tirix.lower after Lower.lower; returns a TESSERAE_LOWER_* code. */
+int tesserae_tirix_lower(const tesserae_kernel_spec* spec, tesserae_tirix** out);
+/* Text -> program; -1 with a message naming the line on a malformed text. */
+int tesserae_tirix_parse(const char* text, tesserae_tirix** out);
+void tesserae_tirix_free(tesserae_tirix* program);
+/* Program -> text (malloc'ed; caller frees). */
+char* tesserae_tirix_print(const tesserae_tirix* program);
+/* Tirix_verify.verify: number of errors (0 = Ok); *errors gets the messages, newline-separated (malloc'ed; caller
+ * frees), the reference's wording: "undefined variable 'x'", "unknown tensor 't' in copy.src", "SFor 'i' has zero
+ * step", "SPipeline has invalid stage count 0", "SWarpGroup role not in cluster warp_roles", ... */
+int tesserae_tirix_verify(const tesserae_tirix* program, char** errors);
+/* How many operations of the named kind ("Copy", "Mma", "MbarWaitParity", "TmemAlloc", ...) the program holds. */
+int tesserae_tirix_count_ops(const tesserae_tirix* program, const char* op_name);
+/* Tirix_emit.emit: program -> the record of source sections (release with tesserae_backend_output_free). */
+int tesserae_tirix_emit(const tesserae_tirix* program, tesserae_backend_output* out);
+
 /* Compile.result (lib/runtime/compile.ml:4-9), with a cubin image instead of PTX. */
 typedef struct tesserae_compile_result {
     char* kernel_name;
@@ -451,6 +477,10 @@ int tesserae_nccl_all_reduce_f32(void* comm, const void* send, void* recv, size_
  * Buffers 16-byte aligned; asynchronous on `stream`. */
 int tesserae_reduce_cast_bf16(const void* parts_f32, int n_parts, size_t part_stride_elems, float alpha,
                               void* out_bf16, size_t n_elems, void* stream);
+/* out[i] = bf16(alpha * acc[i]) and acc[i] = 0, in one pass: the step after a K-split GEMM whose epilogue ADDED the
+ * partial tiles into `acc` (spec.scatter = 2); the buffer is left holding the zeros its next use needs.
+ * Buffers 16-byte aligned; asynchronous on `stream`. */
+int tesserae_cast_clear_bf16(void* acc_f32, float alpha, void* out_bf16, size_t n_elems, void* stream);
 /* Scratch (global memory beyond inputs and outputs) the K-split entry points need: k_splits fp32 M x N partials. */
 size_t tesserae_gemm_ksplit_scratch_bytes(int64_t m, int64_t n, int k_splits);
 /* Partial products only: slice s of K (K/k_splits wide) -> scratch[s] (fp32 M x N).  The plan must be an
@@ -473,9 +503,12 @@ int tesserae_gemm_ksplit_run(tesserae_gemm_plan* plan, const void* a, const void
  * dst[g]; a TMA reduce, still a store-type operation): every source GPU passes the SAME dst[g] for owner g, the
  * buffers must hold zeros when the first contribution arrives, and after the barrier dst[own] already is the
  * reduce-scattered fp32 sum, so only tesserae_reduce_cast_bf16 with n_parts = 1 remains.  The contributions of
- * more than two GPUs meet in no fixed order: the sum may differ in the last place between runs. */
+ * more than two GPUs meet in no fixed order: the sum may differ in the last place between runs.
+ * start_owner: the owner whose rows this GPU computes (and sends) first; the others follow round robin.  Give every
+ * source GPU a different one (its own rank): GPUs that walk the tiles in the same order would all send to the same
+ * owner at the same time and queue up on that owner's NVLink ingress.  0 is always valid. */
 int tesserae_gemm_ksplit_scatter(tesserae_gemm_plan* plan, const void* a, const void* b, void* const* dst, int n_dst,
-                                 int64_t rows_per_owner, int64_t m, int64_t n, int64_t k, void* stream);
+                                 int64_t rows_per_owner, int start_owner, int64_t m, int64_t n, int64_t k, void* stream);
 /* tesserae_gemm_ksplit_run without caller scratch and without any allocation.  It has no counterpart in
  * the reference.  It is for hosts that cannot call cudaMalloc at the moment they need the GEMM: a process
  * whose own allocator already owns nearly all GPU memory (a raw cudaMalloc would fail there), or a serving

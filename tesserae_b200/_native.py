@@ -147,6 +147,13 @@ SIGNATURES = {
     "tesserae_kernel_desc_grid": (C.c_int, [C.POINTER(KernelDescC), C.c_int64, C.c_int64, _IP, _IP, _IP]),
     "tesserae_backend_emit": (C.c_int, [C.POINTER(KernelSpecC), C.POINTER(BackendOutputC)]),
     "tesserae_backend_output_free": (None, [C.POINTER(BackendOutputC)]),
+    "tesserae_tirix_lower": (C.c_int, [C.POINTER(KernelSpecC), C.POINTER(C.c_void_p)]),
+    "tesserae_tirix_parse": (C.c_int, [C.c_char_p, C.POINTER(C.c_void_p)]),
+    "tesserae_tirix_free": (None, [C.c_void_p]),
+    "tesserae_tirix_print": (C.c_void_p, [C.c_void_p]),
+    "tesserae_tirix_verify": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
+    "tesserae_tirix_count_ops": (C.c_int, [C.c_void_p, C.c_char_p]),
+    "tesserae_tirix_emit": (C.c_int, [C.c_void_p, C.POINTER(BackendOutputC)]),
     "tesserae_compile_to_source": (C.c_int, [C.POINTER(KernelSpecC), C.POINTER(CompileResultC)]),
     "tesserae_compile_to_cubin": (C.c_int, [C.POINTER(KernelSpecC), C.POINTER(CompileResultC)]),
     "tesserae_compile_result_free": (None, [C.POINTER(CompileResultC)]),
@@ -203,11 +210,12 @@ SIGNATURES = {
     "tesserae_wait_selftest": (C.c_int, [C.c_int64, C.POINTER(C.c_uint32), C.POINTER(C.c_int64)]),
     "tesserae_shard_range": (C.c_int, [C.c_int64, C.c_int, C.c_int, C.c_int64, _I64P, _I64P]),
     "tesserae_reduce_cast_bf16": (C.c_int, [C.c_void_p, C.c_int, C.c_size_t, C.c_float, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "tesserae_cast_clear_bf16": (C.c_int, [C.c_void_p, C.c_float, C.c_void_p, C.c_size_t, C.c_void_p]),
     "tesserae_gemm_ksplit_scratch_bytes": (C.c_size_t, [C.c_int64, C.c_int64, C.c_int]),
     "tesserae_gemm_ksplit_partials": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_int64,
                                                 C.c_int64, C.c_int64, C.c_int, C.c_void_p]),
     "tesserae_gemm_ksplit_scatter": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p), C.c_int, C.c_int64,
-                                               C.c_int64, C.c_int64, C.c_int64, C.c_void_p]),
+                                               C.c_int, C.c_int64, C.c_int64, C.c_int64, C.c_void_p]),
     "tesserae_gemm_ksplit_run": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t,
                                            C.c_float, C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_void_p]),
     "tesserae_gemm_ksplit_noalloc_max_elems": (C.c_size_t, []),

@@ -87,6 +87,61 @@ def backend_emit(spec: KernelSpec) -> BackendOutput:
     return BackendOutput(**vals)
 
 
+class Tirix:
+    """A Tirix program (tesserae_tirix_*): lowered from a spec or parsed from its text form."""
+
+    def __init__(self, handle):
+        self._h = handle
+
+    @classmethod
+    def lower(cls, spec: KernelSpec) -> "Tirix":
+        """Desc_to_tirix.lower (lib/tirix/desc_to_tirix.ml:466-508) after Lower.lower."""
+        h = C.c_void_p()
+        rc = N.lib().tesserae_tirix_lower(C.byref(spec.to_c()), C.byref(h))
+        if rc != 0:
+            raise LowerError(rc, N.last_error())
+        return cls(h)
+
+    @classmethod
+    def parse(cls, text: str) -> "Tirix":
+        h = C.c_void_p()
+        if N.lib().tesserae_tirix_parse(text.encode(), C.byref(h)) != 0:
+            raise ValueError(N.last_error())
+        return cls(h)
+
+    def text(self) -> str:
+        return N.take_string(N.lib().tesserae_tirix_print(self._h))
+
+    def verify(self) -> list:
+        """Tirix_verify.verify (lib/tirix/tirix_verify.ml:9-183): [] when Ok, else the error messages."""
+        e = C.c_void_p()
+        n = N.lib().tesserae_tirix_verify(self._h, C.byref(e))
+        msgs = N.take_string(e.value).split("\n") if e.value else []
+        assert n == len(msgs)
+        return msgs
+
+    def count_ops(self, name: str) -> int:
+        return N.lib().tesserae_tirix_count_ops(self._h, name.encode())
+
+    def emit(self) -> "BackendOutput":
+        """Tirix_emit.emit (lib/tirix/tirix_emit.ml:481-501)."""
+        out = N.BackendOutputC()
+        rc = N.lib().tesserae_tirix_emit(self._h, C.byref(out))
+        if rc != 0:
+            raise TesseraeError(N.last_error())
+        vals = {f: (C.string_at(getattr(out, f)).decode() if getattr(out, f) else "") for f, _ in out._fields_}
+        N.lib().tesserae_backend_output_free(C.byref(out))
+        return BackendOutput(**vals)
+
+    def __del__(self):
+        try:
+            if self._h:
+                N.lib().tesserae_tirix_free(self._h)
+                self._h = None
+        except Exception:
+            pass
+
+
 @dataclass
 class CompileResult:
     kernel_name: str
@@ -162,12 +217,12 @@ class GemmPlan:
         check(N.lib().tesserae_gemm_ksplit_partials(self._h, _ptr(a), _ptr(b), _ptr(scratch), scratch_bytes, m, n, k,
                                                     k_splits, C.c_void_p(stream or 0)), "gemm_ksplit_partials")
 
-    def ksplit_scatter(self, a, b, dst_ptrs, rows_per_owner, m, n, k, stream=None) -> None:
+    def ksplit_scatter(self, a, b, dst_ptrs, rows_per_owner, m, n, k, stream=None, start_owner: int = 0) -> None:
         """fp32 partial product with rows [g*rows_per_owner, ...) stored to dst_ptrs[g] (device addresses, local or
         peer-mapped): the K-split GEMM with the scatter half of the reduce-scatter in its epilogue."""
         arr = (C.c_void_p * len(dst_ptrs))(*[int(p) for p in dst_ptrs])
-        check(N.lib().tesserae_gemm_ksplit_scatter(self._h, _ptr(a), _ptr(b), arr, len(dst_ptrs), rows_per_owner, m, n, k,
-                                                   C.c_void_p(stream or 0)), "gemm_ksplit_scatter")
+        check(N.lib().tesserae_gemm_ksplit_scatter(self._h, _ptr(a), _ptr(b), arr, len(dst_ptrs), rows_per_owner, start_owner,
+                                                   m, n, k, C.c_void_p(stream or 0)), "gemm_ksplit_scatter")
 
     def ksplit_run(self, a, b, c, scratch, scratch_bytes, m, n, k, k_splits=1, alpha: float = 1.0, stream=None) -> None:
         """K-split GEMM on one GPU: partials into scratch, then sum + bf16 cast into c."""
@@ -221,6 +276,11 @@ def reduce_cast_bf16(parts, n_parts: int, part_stride: int, out, n: int, alpha: 
     """out[i] = bf16(alpha * sum_p parts[p * part_stride + i]) on device buffers."""
     check(N.lib().tesserae_reduce_cast_bf16(_ptr(parts), n_parts, part_stride, alpha, _ptr(out), n,
                                             C.c_void_p(stream or 0)), "reduce_cast_bf16")
+
+
+def cast_clear_bf16(acc, out, n: int, alpha: float = 1.0, stream=None) -> None:
+    """out[i] = bf16(alpha * acc[i]); acc[i] = 0 (device buffers)."""
+    check(N.lib().tesserae_cast_clear_bf16(_ptr(acc), alpha, _ptr(out), n, C.c_void_p(stream or 0)), "cast_clear_bf16")
 
 
 def quantize_fp8_rows(x, q, scale, m: int, k: int, stream=None) -> None:

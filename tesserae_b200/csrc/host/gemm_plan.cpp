@@ -501,7 +501,7 @@ int tesserae_gemm_ksplit_partials(tesserae_gemm_plan* p, const void* a, const vo
 }
 
 int tesserae_gemm_ksplit_scatter(tesserae_gemm_plan* p, const void* a, const void* b, void* const* dst, int n_dst,
-                                 int64_t rows_per_owner, int64_t m, int64_t n, int64_t k, void* stream) {
+                                 int64_t rows_per_owner, int start_owner, int64_t m, int64_t n, int64_t k, void* stream) {
     if (!p || !a || !b || !dst) return fail("ksplit_scatter: null argument");
     if (int drc = check_plan_device(p, "ksplit_scatter")) return drc;
     const KernelConfig& cfg = p->cfg;
@@ -510,6 +510,7 @@ int tesserae_gemm_ksplit_scatter(tesserae_gemm_plan* p, const void* a, const voi
     if (rows_per_owner <= 0 || rows_per_owner % 128 != 0) return fail("ksplit_scatter: rows_per_owner must be a positive multiple of 128");
     if (m <= 0 || n <= 0 || k <= 0 || m > INT32_MAX || n > INT32_MAX || k > INT32_MAX) return fail("ksplit_scatter: bad dimensions");
     if (int64_t(n_dst) * rows_per_owner < m) return fail("ksplit_scatter: n_dst * rows_per_owner must cover M");
+    if (start_owner < 0 || start_owner >= n_dst) return fail("ksplit_scatter: start_owner must be in [0, n_dst)");
     const int ebits = tesserae::spec::elem_bits(cfg.elem);
     if ((k * ebits / 8) % 16 != 0 || (n * 4) % 16 != 0) return fail("ksplit_scatter: K * element size and N * 4 must be multiples of 16 bytes");
     alignas(64) unsigned char tm_a[128], tm_b[128];
@@ -534,12 +535,14 @@ int tesserae_gemm_ksplit_scatter(tesserae_gemm_plan* p, const void* a, const voi
     const int block[3] = {cfg.threads, 1, 1};
     const int cluster[3] = {cfg.cta_group, 1, 1};
     const int mi = int(m), ni = int(n), ki = int(k), rpo = int(rows_per_owner), gmi = pick_group_m(cfg, m, k);
+    const int rot = int((int64_t(start_owner) * rows_per_owner) / (128 * cfg.cta_group));   // M-tiles in front of that owner's rows
     const void* no_bias = nullptr;
     const float one = 1.0f;
     const tesserae_launch_arg args[] = {
-        {tm_a, 128}, {tm_b, 128}, {&tm_c, sizeof tm_c}, {&rpo, sizeof(int)}, {&no_bias, sizeof(void*)}, {&one, sizeof(float)},
-        {&mi, sizeof(int)}, {&ni, sizeof(int)}, {&ki, sizeof(int)}, {&gmi, sizeof(int)}, {&p->d_status, sizeof(void*)}};
-    return tesserae_launch_kernel_ex(p->function, grid, block, cluster, cfg.smem_bytes, stream, args, 11);
+        {tm_a, 128}, {tm_b, 128}, {&tm_c, sizeof tm_c}, {&rpo, sizeof(int)}, {&rot, sizeof(int)}, {&no_bias, sizeof(void*)},
+        {&one, sizeof(float)}, {&mi, sizeof(int)}, {&ni, sizeof(int)}, {&ki, sizeof(int)}, {&gmi, sizeof(int)},
+        {&p->d_status, sizeof(void*)}};
+    return tesserae_launch_kernel_ex(p->function, grid, block, cluster, cfg.smem_bytes, stream, args, 12);
 }
 
 int tesserae_gemm_ksplit_run(tesserae_gemm_plan* p, const void* a, const void* b, void* c_bf16, void* scratch,

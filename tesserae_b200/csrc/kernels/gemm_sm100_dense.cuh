@@ -41,6 +41,10 @@
 //                    M/G x N fp32 array per owner, which must hold zeros beforehand; no sum pass follows, only the
 //                    cast.  The order in which the G contributions meet is not fixed, so beyond two GPUs the fp32
 //                    sum can differ in the last place from run to run.
+//                    m_rotate (scattered kernels): the tile order is rotated by this many M-tiles.  GPUs that run
+//                    the same schedule would all send to the same owner at the same time (the rows of the first
+//                    raster group) and queue up on that owner's NVLink ingress; with a different rotation per
+//                    source GPU the owners are visited round robin.
 #pragma once
 
 #ifndef TS_SCATTER
@@ -96,7 +100,7 @@ extern "C" __global__ void __launch_bounds__(192, 1)
 TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
                const __grid_constant__ TsTensorMap tmap_b,
 #if TS_SCATTER
-               const __grid_constant__ TsTensorMapArray8 tmap_cs, int rows_per_owner,
+               const __grid_constant__ TsTensorMapArray8 tmap_cs, int rows_per_owner, int m_rotate,
 #else
                const __grid_constant__ TsTensorMap tmap_c,
 #endif
@@ -168,6 +172,9 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
             for (ts_u32 t = first_tile; t < num_tiles && ok; t += tile_step) {
                 ts_u32 m_blk, n_blk;
                 ts_decode_tile(t, num_m, num_n, (ts_u32)group_m, m_blk, n_blk);
+#if TS_SCATTER
+                m_blk = (m_blk + (ts_u32)m_rotate) % num_m;
+#endif
                 const int a_row = (int)(m_blk * kTileM + cta_rank * kBlockM);
                 const int b_row = (int)(n_blk * kBlockN + cta_rank * kLoadN);
                 for (ts_u32 kb = 0; kb < num_k_blocks; ++kb, ++it) {
@@ -251,6 +258,9 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
         for (ts_u32 t = first_tile; t < num_tiles && ok; t += tile_step, ++tile_iter) {
             ts_u32 m_blk, n_blk;
             ts_decode_tile(t, num_m, num_n, (ts_u32)group_m, m_blk, n_blk);
+#if TS_SCATTER
+            m_blk = (m_blk + (ts_u32)m_rotate) % num_m;
+#endif
             const ts_u32 acc = tile_iter % kNumAcc;
             const ts_u32 acc_ph = (tile_iter / kNumAcc) & 1u;
             if (!ts_mbar_wait(tmem_full_bar + 8 * acc, acc_ph)) {

@@ -8,6 +8,7 @@
 
 #include <cuda_runtime.h>
 #include <cstdint>
+#include <string>
 
 using tesserae::fail;
 
@@ -47,7 +48,47 @@ __global__ void __launch_bounds__(256) reduce_cast_kernel(const float* __restric
     }
 }
 
+// out = bf16(alpha * acc) and acc = 0 in one pass: the step after the adding K-split epilogue, whose accumulation
+// buffer must hold zeros again before its next use.  Reads 4 bytes, writes 2 + 4 per element.
+__global__ void __launch_bounds__(256) cast_clear_kernel(float* __restrict__ acc, float alpha, uint16_t* __restrict__ out, size_t n) {
+    const size_t n8 = n / 8;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += stride) {
+        float4* q = reinterpret_cast<float4*>(acc) + 2 * i;
+        const float4 a = q[0], b = q[1];
+        q[0] = zero; q[1] = zero;
+        uint4 o;
+        o.x = pack_bf16x2(alpha * a.x, alpha * a.y); o.y = pack_bf16x2(alpha * a.z, alpha * a.w);
+        o.z = pack_bf16x2(alpha * b.x, alpha * b.y); o.w = pack_bf16x2(alpha * b.z, alpha * b.w);
+        reinterpret_cast<uint4*>(out)[i] = o;
+    }
+    const size_t t = n8 * 8 + (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t < n) {
+        out[t] = (uint16_t)(pack_bf16x2(alpha * acc[t], 0.f) & 0xFFFFu);
+        acc[t] = 0.f;
+    }
+}
+
 }  // namespace
+
+extern "C" int tesserae_cast_clear_bf16(void* acc_f32, float alpha, void* out_bf16, size_t n_elems, void* stream) {
+    if (!acc_f32 || !out_bf16) return fail("cast_clear: null argument");
+    if (n_elems == 0) return 0;
+    if ((reinterpret_cast<uintptr_t>(acc_f32) & 15u) || (reinterpret_cast<uintptr_t>(out_bf16) & 15u))
+        return fail("cast_clear: buffers must be 16-byte aligned");
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const size_t want = (n_elems / 8 + 255) / 256 + 1;
+    const size_t cap = (size_t)sms * 8;
+    const unsigned grid = (unsigned)(want < cap ? want : cap);
+    cast_clear_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<float*>(acc_f32), alpha,
+                                                                           static_cast<uint16_t*>(out_bf16), n_elems);
+    cudaError_t rc = cudaGetLastError();
+    if (rc != cudaSuccess) return fail(std::string("cast_clear launch: ") + cudaGetErrorString(rc));
+    return 0;
+}
 
 extern "C" int tesserae_reduce_cast_bf16(const void* parts, int n_parts, size_t part_stride_elems, float alpha,
                                          void* out_bf16, size_t n_elems, void* stream) {

@@ -53,7 +53,7 @@ def main():
     slot = rows * n * 4
     results = []
     for _ in range(2):                                                     # twice: the staging slots are reused
-        scat.ksplit_scatter(a, b, [hdl.buffer_ptrs[g] + rank * slot for g in range(world)], rows, m, n, k, stream=s)
+        scat.ksplit_scatter(a, b, [hdl.buffer_ptrs[g] + rank * slot for g in range(world)], rows, m, n, k, stream=s, start_owner=rank)
         hdl.barrier(channel=0)
         api.reduce_cast_bf16(stag, world, rows * n, c_fused, rows * n, stream=s)
         hdl.barrier(channel=0)
@@ -72,12 +72,12 @@ def main():
     radd = api.GemmPlan(api.KernelSpec(name="gemm_bf16_cg2_f32_scatter_add", elem=api.BF16, tile=(128, 256, 64),
                                        cta_group=2, out_elem=api.F32, scatter=2))
     c_add = torch.empty((rows, n), dtype=torch.bfloat16, device=dev)
+    acc.zero_()
     for _ in range(2):
-        acc.zero_()
         hdl2.barrier(channel=0)
-        radd.ksplit_scatter(a, b, [hdl2.buffer_ptrs[g] for g in range(world)], rows, m, n, k, stream=s)
+        radd.ksplit_scatter(a, b, [hdl2.buffer_ptrs[g] for g in range(world)], rows, m, n, k, stream=s, start_owner=rank)
         hdl2.barrier(channel=0)
-        api.reduce_cast_bf16(acc, 1, 0, c_add, rows * n, stream=s)
+        api.cast_clear_bf16(acc, c_add, rows * n, stream=s)          # casts and leaves the zeros the next round needs
         hdl2.barrier(channel=0)
         torch.cuda.synchronize()
         err = O.rel_error(c_add.float().cpu().numpy(), want)["max_rel"]

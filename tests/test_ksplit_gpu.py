@@ -121,7 +121,7 @@ def test_scatter_epilogue_matches_plain_partial(torch_cuda, plan_f32):
     scat = api.GemmPlan(api.KernelSpec(name="gemm_bf16_cg2_f32_scatter", elem=api.BF16, tile=(128, 256, 64), cta_group=2,
                                        out_elem=api.F32, scatter=1))
     dst = [t.full((rpo, n), float("nan"), dtype=t.float32, device="cuda") for _ in range(owners)]
-    scat.ksplit_scatter(a, b, [d.data_ptr() for d in dst], rpo, m, n, k, stream=s)
+    scat.ksplit_scatter(a, b, [d.data_ptr() for d in dst], rpo, m, n, k, stream=s, start_owner=2)   # a rotated tile order
     assert scat.status() == 0 and plan_f32.status() == 0
     for g in range(owners):
         rows = min(rpo, m - g * rpo)
@@ -193,3 +193,16 @@ def test_scatter_add_epilogue_matches_plain_partial(torch_cuda, plan_f32):
             assert t.equal(dst[g][:rows], plain[g * rpo:g * rpo + rows] * times), (g, times)
             assert (dst[g][rows:] == 0).all()              # nothing added past the owner's slice
     radd.close()
+
+
+def test_cast_clear(torch_cuda):
+    """tesserae_cast_clear_bf16: the cast of the adding epilogue's buffer, which leaves the buffer zeroed; same
+    rounding as tesserae_reduce_cast_bf16 of one partial, ragged length included."""
+    t = torch_cuda
+    for n in (8 * 1024 + 5, 3, 1 << 20):
+        acc = t.randn(n + 3, device="cuda")[:n].contiguous() if n % 4 else t.randn(n, device="cuda")
+        want = t.empty(n, dtype=t.bfloat16, device="cuda")
+        api.reduce_cast_bf16(acc, 1, 0, want, n, alpha=0.5, stream=t.cuda.current_stream().cuda_stream)
+        got = t.full((n,), float("nan"), dtype=t.bfloat16, device="cuda")
+        api.cast_clear_bf16(acc, got, n, alpha=0.5, stream=t.cuda.current_stream().cuda_stream)
+        assert t.equal(got.view(t.int16), want.view(t.int16)) and not acc.any()
