@@ -191,8 +191,9 @@ def workload_config(name, w, gpus, exchange="fused"):
 class Workload:
     """Builds device + pinned host operands for this rank's shard; step() launches the hot path once."""
 
-    def __init__(self, name, w, rank, world, dev, exchange="fused"):
+    def __init__(self, name, w, rank, world, dev, exchange="fused", tuning=""):
         self.exchange = exchange
+        self.tuning = tuning          # the spec's tuning string ("NAME=VALUE;..."), for A/B runs from the command line
         import numpy as np
         import torch
         from oracle import gemm_oracle as O
@@ -230,7 +231,8 @@ class Workload:
         self.c_host = t.empty((self.m, self.n), dtype=t.bfloat16).pin_memory()
         self.c = t.empty((self.m, self.n), dtype=t.bfloat16, device=self.dev)
         self.plan = api.GemmPlan(api.KernelSpec(name=f"gemm_bf16_cg2_bf16_b{int(w['bias'])}", elem=api.BF16,
-                                                tile=(128, 256, 64), cta_group=2, out_elem=api.BF16, has_bias=int(w["bias"])))
+                                                tile=(128, 256, 64), cta_group=2, out_elem=api.BF16, has_bias=int(w["bias"]),
+                                                tuning=self.tuning))
         self.step = lambda: self.plan.run(self.a, self.b, self.c, self.bias, 1.0, self.m, self.n, self.k, stream=self.stream)
         self.e2e_step = lambda: self.plan.run_host(self.a_host, self.b_host, self.c_host, self.bias_host, 1.0,
                                                    self.m, self.n, self.k)
@@ -252,8 +254,17 @@ class Workload:
         self.ga = self.gb = 1.0
         self.c = t.empty((self.m, self.n), dtype=t.bfloat16, device=self.dev)
         self.plan = api.GemmPlan(api.KernelSpec(name="gemm_fp8blk_cg2_n256", elem=api.F8E4M3, tile=(128, 256, 128),
-                                                cta_group=2, out_elem=api.BF16, scale_mode=api.SCALE_FP8_BLOCK))
+                                                cta_group=2, out_elem=api.BF16, scale_mode=api.SCALE_FP8_BLOCK,
+                                                tuning=self.tuning))
         self._finish_scaled()
+        # Stream-K tail: when this rank's tile count leaves a nearly empty last wave the plan asks for a workspace and
+        # the device step goes through the workspace entry point.
+        self.tail_bytes = self.plan.tail_workspace_bytes(self.m, self.n, self.k)
+        if self.tail_bytes:
+            self.tail_ws = t.zeros(self.tail_bytes // 4, dtype=t.float32, device=self.dev)
+            self.launches_per_step = 2
+            self.step = lambda: self.plan.run_scaled_ws(self.a, self.b, self.c, self.sa, self.sb, self.tail_ws, self.tail_bytes,
+                                                        None, 1.0, self.m, self.n, self.k, stream=self.stream)
 
     def _setup_nvfp4(self):
         t, api, w = self.torch, self.api, self.w
@@ -274,7 +285,8 @@ class Workload:
         del qb, sfb
         self.c = t.empty((self.m, self.n), dtype=t.bfloat16, device=self.dev)
         self.plan = api.GemmPlan(api.KernelSpec(name="gemm_nvfp4_cg2_n256", elem=api.F4E2M1, tile=(128, 256, 256),
-                                                cta_group=2, out_elem=api.BF16, scale_mode=api.SCALE_NVFP4))
+                                                cta_group=2, out_elem=api.BF16, scale_mode=api.SCALE_NVFP4,
+                                                tuning=self.tuning))
         self._finish_scaled()
 
     def _finish_scaled(self):
@@ -500,7 +512,7 @@ def measure(name, w, rank, local_rank, world, dev, args, exchange="fused", extra
     oracle check, reduces over the ranks (max) and returns the record (on every rank) plus the live workload."""
     import torch
     import torch.distributed as dist
-    wl = Workload(name, w, rank, world, dev, exchange=exchange)
+    wl = Workload(name, w, rank, world, dev, exchange=exchange, tuning=args.tuning if name == args.workload else "")
 
     def sync_all():
         torch.cuda.synchronize()
@@ -589,6 +601,7 @@ def measure(name, w, rank, local_rank, world, dev, args, exchange="fused", extra
         "gpu_launches": args.steps * wl.launches_per_step,
         "clocks": clocks,
         "kernel_status": int(status), "max_rel_err_vs_oracle_sample": max_rel,
+        "stream_k_tail_workspace_bytes": int(getattr(wl, "tail_bytes", 0)),
     }
     if split:
         rec["ksplit"] = {"exchange": exchange if world > 1 else "none", "gemm_ms": gemm_ms,
@@ -602,7 +615,7 @@ def pcie_probe(wl, world, dev):
     the end-to-end leg): one plain copy of A up and of C back, CUDA events; min / max over the ranks."""
     import torch
     import torch.distributed as dist
-    src, dst = wl.a_host, wl.c_host
+    src, dst = (wl.a_host if hasattr(wl, "a_host") else wl.h_in[1]), wl.c_host     # (scaled workloads: the B operand)
     d_in = torch.empty_like(src, device=dev)
     d_out = torch.empty_like(dst, device=dev)
     out = []
@@ -665,6 +678,7 @@ def main():
                     help="also measure fp8_block, nvfp4 and bf16_ksplit in the same process (default: all for the "
                          "headline workload, none otherwise)")
     ap.add_argument("--sustained-seconds", type=float, default=1.0)
+    ap.add_argument("--tuning", default="", help="tuning string of the main workload's kernel spec, e.g. GROUP_M=4 or TAIL_SPLITS=1")
     ap.add_argument("--ksplit-exchange", default="reduce", choices=["reduce", "fused", "nccl"],
                     help="K-split at 2+ GPUs: tiles added into the owner's buffer by the GEMM's own stores (reduce), stored "
                          "to per-source slots and summed by the owner (fused), or NCCL reduce-scatter of plain partials")

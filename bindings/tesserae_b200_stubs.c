@@ -9,7 +9,7 @@
  * Status: NOT linked against an OCaml runtime.  No OCaml toolchain exists where this library is built, so this
  * file is only checked to parse and type-check (gcc -fsyntax-only -Wall -Wextra -Werror) against a minimal
  * stand-in for <caml/...> kept with the tests; what it proves is that the glue calls tesserae_* with the right
- * argument types.  A maintainer with the toolchain adds it as `foreign_stubs`.
+ * argument types.  A maintainer with the toolchain adds it as `foreign_stubs` in the dune files of lib/runtime and lib/kernel.
  *
  * Conventions kept from the reference: a failing call raises Failure with the library's message
  * (kernel_launch_stubs.c:8-19); `compile` is the one call that returns a result instead of raising

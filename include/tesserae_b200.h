@@ -245,6 +245,7 @@ typedef struct tesserae_kernel_spec {
      *   FP8_SPLIT=0|1          block-scaled FP8: one MMA chain per tile width / per 128 columns
      * An unknown name or a value out of range fails with IncompatibleTile. */
     const char* tuning;
+    int grouped;     /* 1: the kernel walks a list of problems (tesserae_gemm_run_grouped); unscaled kernels, no scatter */
 } tesserae_kernel_spec;
 
 /* Kernel_desc.t (lib/kernel/kernel_desc.ml:12-26), flattened to integers. */
@@ -427,6 +428,46 @@ typedef struct tesserae_gemm_scales {
 int tesserae_gemm_run_scaled(tesserae_gemm_plan* plan, const void* a, const void* b, void* c,
                              const tesserae_gemm_scales* scales, const void* bias,
                              float alpha, int64_t m, int64_t n, int64_t k, void* stream);
+/* ------------------------------------------------------------------ stream-K tail (FP8 block-scaled)
+ * tesserae_gemm_run_scaled with a workspace: when the problem's tile count leaves a nearly empty last wave, the tiles
+ * past the last whole wave are split into ranges of K blocks that all CTAs share; their fp32 partial sums are added
+ * into the workspace and a closing kernel adds the bias, casts into C and clears the workspace again.  The role is the
+ * one the reference reserves for a scheduler (lib/pipeline/cluster.mli:17-21); it has no counterpart there.
+ *   tesserae_gemm_tail_workspace_bytes: bytes the call below needs for this problem on this plan (0: no tail is used,
+ *   the workspace may be NULL).  By default a tail is used only when the left-over tiles would occupy at most one
+ *   cluster in sixteen after at least one whole wave (where it was measured to pay); tuning TAIL_SPLITS=n (n >= 2)
+ *   asks for it whenever the left-over tiles fill at most half the clusters, with at most n ranges per tile;
+ *   TAIL_SPLITS=1 never splits.
+ *   The workspace must be 128-byte aligned and ZERO-FILLED before its first use; every call leaves it zero-filled.
+ *   After a call whose tesserae_gemm_status is not 0, clear it again.
+ * The additions into the workspace happen in no fixed order: the tail tiles' results can differ in the last bit from
+ * run to run and from tesserae_gemm_run_scaled; all other tiles are bit-identical. */
+size_t tesserae_gemm_tail_workspace_bytes(const tesserae_gemm_plan* plan, int64_t m, int64_t n, int64_t k);
+int tesserae_gemm_run_scaled_ws(tesserae_gemm_plan* plan, const void* a, const void* b, void* c,
+                                const tesserae_gemm_scales* scales, const void* bias,
+                                float alpha, int64_t m, int64_t n, int64_t k,
+                                void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------ grouped GEMM
+ * Many independent problems C_i = alpha * A_i . B_i^T (+ bias_i) in one launch (the role the reference reserves for
+ * its scheduler warp, lib/pipeline/cluster.mli:17-21, lib/kernel/kernel_desc.ml:135; it builds none).  The plan's spec
+ * must have grouped = 1.  The tiles of all problems are numbered consecutively and dealt to the persistent CTAs, so a
+ * wave holds tiles of several problems and a list of small or ragged problems is not quantised one by one.
+ * Layouts per problem as for tesserae_gemm_run; sizes may differ from problem to problem.
+ * `workspace` is device memory of tesserae_gemm_grouped_workspace_bytes(n_problems) bytes (the problem table: tensor
+ * maps and sizes, written by this call with an asynchronous copy on `stream`); it must stay untouched until the launch
+ * has finished.  Asynchronous on `stream`. */
+typedef struct tesserae_gemm_problem {
+    const void* a;      /* M x K, row-major */
+    const void* b;      /* N x K, row-major */
+    void* c;            /* M x N, row-major */
+    const void* bias;   /* bf16[N] or NULL (must be given when the kernel was built with a bias) */
+    int64_t m, n, k;
+} tesserae_gemm_problem;
+size_t tesserae_gemm_grouped_workspace_bytes(int n_problems);
+int tesserae_gemm_run_grouped(tesserae_gemm_plan* plan, const tesserae_gemm_problem* problems, int n_problems,
+                              float alpha, void* workspace, size_t workspace_bytes, void* stream);
+
 /* ------------------------------------------------------------------ quantisers (the step before a block-scaled GEMM)
  * fp32 device source -> the operand and scale layouts tesserae_gemm_run_scaled takes.  New surface: the
  * reference has no narrow float element.  Asynchronous on `stream` unless noted.  Recipes:

@@ -16,7 +16,7 @@ class KernelSpecC(C.Structure):
     _fields_ = [("name", C.c_char_p), ("arch", C.c_int), ("elem", C.c_int),
                 ("tile_m", C.c_int), ("tile_n", C.c_int), ("tile_k", C.c_int), ("stages", C.c_int),
                 ("cta_group", C.c_int), ("out_elem", C.c_int), ("has_bias", C.c_int), ("scale_mode", C.c_int),
-                ("scatter", C.c_int), ("tuning", C.c_char_p)]
+                ("scatter", C.c_int), ("tuning", C.c_char_p), ("grouped", C.c_int)]
 
 
 class KernelDescC(C.Structure):
@@ -75,6 +75,11 @@ class TileOpC(C.Structure):
     _fields_ = [("atom", MmaAtomC), ("thread_layout_size", C.c_int64), ("warp_layout_size", C.c_int64),
                 ("tiler_m", C.c_int64), ("tiler_n", C.c_int64), ("accum_loc", C.c_int), ("has_tmem", C.c_int),
                 ("tmem_cta_group", C.c_int), ("tmem_cols", C.c_int), ("tmem_rows", C.c_int), ("double_buf", C.c_int)]
+
+
+class GemmProblemC(C.Structure):
+    _fields_ = [("a", C.c_void_p), ("b", C.c_void_p), ("c", C.c_void_p), ("bias", C.c_void_p),
+                ("m", C.c_int64), ("n", C.c_int64), ("k", C.c_int64)]
 
 
 class LaunchArgC(C.Structure):
@@ -193,6 +198,12 @@ SIGNATURES = {
                                     C.c_int64, C.c_int64, C.c_int64, C.c_void_p]),
     "tesserae_gemm_run_scaled": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(GemmScalesC),
                                            C.c_void_p, C.c_float, C.c_int64, C.c_int64, C.c_int64, C.c_void_p]),
+    "tesserae_gemm_tail_workspace_bytes": (C.c_size_t, [C.c_void_p, C.c_int64, C.c_int64, C.c_int64]),
+    "tesserae_gemm_run_scaled_ws": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(GemmScalesC), C.c_void_p,
+                                              C.c_float, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "tesserae_gemm_grouped_workspace_bytes": (C.c_size_t, [C.c_int]),
+    "tesserae_gemm_run_grouped": (C.c_int, [C.c_void_p, C.POINTER(GemmProblemC), C.c_int, C.c_float, C.c_void_p, C.c_size_t,
+                                            C.c_void_p]),
     "tesserae_quantize_fp8_rows": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]),
     "tesserae_quantize_fp8_blocks": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]),
     "tesserae_nvfp4_scale_bytes": (C.c_size_t, [C.c_int64, C.c_int64]),

@@ -35,6 +35,7 @@ class KernelSpec:
     scale_mode: int = 0
     scatter: int = 0
     tuning: str = ""
+    grouped: int = 0
     _keep: list = field(default_factory=list, repr=False, compare=False)
 
     def to_c(self) -> N.KernelSpecC:
@@ -43,7 +44,7 @@ class KernelSpec:
         tuning = self.tuning.encode() if self.tuning else None
         self._keep.append(tuning)
         return N.KernelSpecC(name, self.arch, self.elem, self.tile[0], self.tile[1], self.tile[2], self.stages,
-                             self.cta_group, self.out_elem, self.has_bias, self.scale_mode, self.scatter, tuning)
+                             self.cta_group, self.out_elem, self.has_bias, self.scale_mode, self.scatter, tuning, self.grouped)
 
 
 class LowerError(Exception):
@@ -212,6 +213,25 @@ class GemmPlan:
         check(N.lib().tesserae_gemm_run_scaled(self._h, _ptr(a), _ptr(b), _ptr(c), C.byref(sc), _ptr(bias), alpha,
                                                m, n, k, C.c_void_p(stream or 0)), "gemm_run_scaled")
 
+    def tail_workspace_bytes(self, m: int, n: int, k: int) -> int:
+        """Bytes of zero-filled workspace run_scaled_ws wants for this problem (0: no stream-K tail is used)."""
+        return N.lib().tesserae_gemm_tail_workspace_bytes(self._h, m, n, k)
+
+    def run_scaled_ws(self, a, b, c, scale_a, scale_b, workspace, workspace_bytes: int, bias=None, alpha: float = 1.0,
+                      m=None, n=None, k=None, stream=None) -> None:
+        """FP8 block-scaled GEMM with a stream-K tail through `workspace` (zero-filled before first use)."""
+        sc = N.GemmScalesC(_ptr(scale_a), _ptr(scale_b), 1.0, 1.0)
+        check(N.lib().tesserae_gemm_run_scaled_ws(self._h, _ptr(a), _ptr(b), _ptr(c), C.byref(sc), _ptr(bias), alpha, m, n, k,
+                                                  _ptr(workspace), workspace_bytes, C.c_void_p(stream or 0)), "gemm_run_scaled_ws")
+
+    def run_grouped(self, problems, workspace, workspace_bytes: int, alpha: float = 1.0, stream=None) -> None:
+        """Grouped GEMM: `problems` is a list of (a, b, c, bias, m, n, k) with device buffers; one launch."""
+        arr = (N.GemmProblemC * len(problems))()
+        for i, (a, b, c, bias, m, n, k) in enumerate(problems):
+            arr[i] = N.GemmProblemC(_ptr(a), _ptr(b), _ptr(c), _ptr(bias), m, n, k)
+        check(N.lib().tesserae_gemm_run_grouped(self._h, arr, len(problems), alpha, _ptr(workspace), workspace_bytes,
+                                                C.c_void_p(stream or 0)), "gemm_run_grouped")
+
     def ksplit_partials(self, a, b, scratch, scratch_bytes, m, n, k, k_splits=1, stream=None) -> None:
         """fp32 partial products of each K slice into scratch[s] (device buffers)."""
         check(N.lib().tesserae_gemm_ksplit_partials(self._h, _ptr(a), _ptr(b), _ptr(scratch), scratch_bytes, m, n, k,
@@ -355,6 +375,10 @@ def shard_range(total: int, parts: int, index: int, align: int = 1):
     b, n = C.c_int64(), C.c_int64()
     check(N.lib().tesserae_shard_range(total, parts, index, align, C.byref(b), C.byref(n)), "shard_range")
     return b.value, n.value
+
+
+def grouped_workspace_bytes(n_problems: int) -> int:
+    return N.lib().tesserae_gemm_grouped_workspace_bytes(n_problems)
 
 
 def ksplit_scratch_bytes(m: int, n: int, k_splits: int = 1) -> int:

@@ -122,6 +122,11 @@ int derive_config(const tesserae_kernel_spec& ks, KernelConfig* cfg, std::string
         if (msg) *msg = "IncompatibleTile: scatter must be 0, 1 (store to per-source slots) or 2 (add into the owner's buffer)";
         return spec::IncompatibleTile;
     }
+    c.grouped = ks.grouped ? 1 : 0;
+    if (c.grouped && (ks.scale_mode != TESSERAE_SCALE_NONE || c.scatter)) {
+        if (msg) *msg = "IncompatibleTile: grouped launches are for the unscaled kernels without scattered output";
+        return spec::IncompatibleTile;
+    }
     if (c.scatter && (ks.scale_mode != TESSERAE_SCALE_NONE || ks.has_bias || c.out_elem != TESSERAE_F32)) {
         if (msg) *msg = "IncompatibleTile: scattered output is for unscaled kernels with fp32 output and no bias";
         return spec::IncompatibleTile;
@@ -145,6 +150,7 @@ int derive_config(const tesserae_kernel_spec& ks, KernelConfig* cfg, std::string
             else if (key == "STORE_BUFS") { ok = v >= 2 && v <= 4; c.store_bufs = v; }
             else if (key == "FP8_PROMO_WARPS") { ok = v == 8 || v == 16; want_promo_warps = v; }
             else if (key == "FP8_SPLIT") { ok = v == 0 || v == 1; c.fp8_split = v; }
+            else if (key == "TAIL_SPLITS") { ok = v >= 0 && v <= 64; c.tail_splits = v; }
             else { if (msg) *msg = "IncompatibleTile: unknown tuning name '" + key + "'"; return spec::IncompatibleTile; }
             if (!ok) {
                 if (msg) *msg = "IncompatibleTile: tuning value out of range: " + key + "=" + std::to_string(v);
@@ -259,6 +265,7 @@ BackendOutput emit(const KernelConfig& c) {
              c.out_elem == TESSERAE_F32 ? 1 : 0, c.has_bias, c.promo_warps ? c.promo_warps : 8, c.desc.swizzle.b);
     o.includes = buf;
     if (c.scatter) o.includes += "#define TS_SCATTER " + std::to_string(c.scatter) + "\n";
+    if (c.grouped) o.includes += "#define TS_GROUPED 1\n";
     if (c.scale_mode == TESSERAE_SCALE_NONE) o.includes += "#define TS_STORE_BUFS " + std::to_string(c.store_bufs) + "\n";
     if (c.scale_mode == TESSERAE_SCALE_FP8_BLOCK) {
         o.includes += std::string("#define TS_FP8_SPLIT ") + (c.fp8_split ? "1\n" : "0\n");
@@ -279,10 +286,11 @@ BackendOutput emit(const KernelConfig& c) {
              "// lib/backend/backend_cute.ml:368-429, cudaLaunchKernelEx with a cluster attribute):\n"
              "//   grid  = (%d * min(tiles, resident clusters), 1, 1)   tiles = ceil(M/%d) * ceil(N/%d)\n"
              "//   block = (%d, 1, 1)   cluster = (%d, 1, 1)   dynamic smem = %d\n"
-             "//   args  = A_tmap, B_tmap, C_tmap (CUtensorMap by value), %sbias, alpha, M, N, K, group_m, status\n"
+             "//   args  = A_tmap, B_tmap, C_tmap (CUtensorMap by value), %sbias, alpha, M, N, K, group_m, %sstatus\n"
              "//   tesserae_launch_kernel_ex(fn, grid, block, cluster, %d, stream, args, %d);\n",
              c.cta_group, c.block_m * c.cta_group, c.block_n, c.threads, c.cta_group, c.smem_bytes,
-             block_fp8 ? "scale_a, scale_b, " : nvfp4 ? "SFA_tmap, SFB_tmap, " : "", c.smem_bytes, (block_fp8 || nvfp4) ? 12 : 10);
+             block_fp8 ? "WS_tmap, scale_a, scale_b, " : nvfp4 ? "SFA_tmap, SFB_tmap, " : "", block_fp8 ? "full_tiles, tail_splits, " : "",
+             c.smem_bytes, block_fp8 ? 15 : nvfp4 ? 12 : 10);
     o.host_launcher = buf;
     o.full_source = o.includes + o.helpers + "\n" + body + "\n" + o.host_launcher;
     return o;

@@ -45,6 +45,11 @@ struct tesserae_gemm_plan {
     size_t ws_cap[6] = {0, 0, 0, 0, 0, 0};
     // Streams and events of the pipelined host-buffer call (copy in / compute / copy out); created on first use.
     static constexpr int kMaxChunks = 32;
+    void* tail_function = nullptr;       // FP8 block-scaled: the kernel that closes a stream-K tail
+    // Pinned host copy of the grouped launch's problem table and the event that says the device has taken it.
+    void* h_table = nullptr;
+    size_t h_table_cap = 0;
+    cudaEvent_t ev_table = nullptr;
     cudaStream_t s_in = nullptr, s_cmp = nullptr, s_out = nullptr;
     cudaEvent_t ev_in[kMaxChunks] = {}, ev_cmp[kMaxChunks] = {}, ev_done = nullptr;
 };
@@ -271,6 +276,8 @@ int tesserae_gemm_plan_create(const tesserae_kernel_spec* ks, tesserae_gemm_plan
     p->compile_ms = cr.duration_ms;
     rc = tesserae_module_load(cr.cubin, &p->module);
     if (rc == 0) rc = tesserae_get_function(p->module, cfg.name.c_str(), &p->function);
+    if (rc == 0 && cfg.scale_mode == TESSERAE_SCALE_FP8_BLOCK)
+        rc = tesserae_get_function(p->module, (cfg.name + "_tail").c_str(), &p->tail_function);
     tesserae_compile_result_free(&cr);
     if (rc != 0) { tesserae_gemm_plan_destroy(p); return rc; }
 
@@ -329,6 +336,8 @@ void tesserae_gemm_plan_destroy(tesserae_gemm_plan* p) {
     for (cudaEvent_t e : p->ev_in) if (e) cudaEventDestroy(e);
     for (cudaEvent_t e : p->ev_cmp) if (e) cudaEventDestroy(e);
     if (p->ev_done) cudaEventDestroy(p->ev_done);
+    if (p->ev_table) cudaEventDestroy(p->ev_table);
+    if (p->h_table) cudaFreeHost(p->h_table);
     if (p->s_in) cudaStreamDestroy(p->s_in);
     if (p->s_cmp) cudaStreamDestroy(p->s_cmp);
     if (p->s_out) cudaStreamDestroy(p->s_out);
@@ -378,16 +387,51 @@ static int pick_group_m(const KernelConfig& cfg, int64_t m, int64_t k) {
     return int(g < 1 ? 1 : g);
 }
 
+// Stream-K tail of the FP8 block-scaled kernel: which tiles are computed whole and into how many ranges of K blocks
+// each of the rest is split.  The tail pays a pass over its tiles (workspace adds, closing kernel) and the fixed cost
+// of a unit, and the few tiles of a nearly empty last wave already run faster than tiles of a full wave (they have
+// the memory system to themselves), so what it wins is small.  Measured on a B200 (8192 x N x 4096, 74 clusters):
+// 2 tiles left over: 2 % faster; 4: even; 8 and 16: 1-2 % slower; problems of less than a wave: 7-37 % slower.
+// By default it is therefore used only when at least one whole wave runs and the tiles left over would occupy at
+// most one cluster in sixteen.  TAIL_SPLITS=n (n >= 2) in the spec's tuning asks for it whenever tiles are left over
+// that fill at most half the clusters (with at most n ranges), which is what the tests use to reach every path.
+struct TailPlan { int64_t full_tiles = 0, tail_tiles = 0; int splits = 1; size_t bytes = 0; };
+static TailPlan plan_tail(const tesserae_gemm_plan* p, int64_t m, int64_t n, int64_t k) {
+    const KernelConfig& cfg = p->cfg;
+    TailPlan t;
+    const int64_t tile_m = 128 * cfg.cta_group;
+    const int64_t tiles = ((m + tile_m - 1) / tile_m) * ((n + cfg.block_n - 1) / cfg.block_n);
+    t.full_tiles = tiles;
+    if (cfg.scale_mode != TESSERAE_SCALE_FP8_BLOCK || cfg.tail_splits == 1) return t;
+    const int64_t clusters = p->max_clusters, nkb = k / 128;
+    const int64_t rest = tiles % clusters;
+    if (rest == 0 || nkb < 4) return t;
+    const bool asked = cfg.tail_splits >= 2;
+    if (asked ? rest * 2 > clusters : (tiles < clusters || rest * 16 > clusters)) return t;
+    int64_t splits = clusters / rest;
+    if (splits > nkb / 2) splits = nkb / 2;              // at least two K blocks per unit
+    if (splits > 16) splits = 16;
+    if (asked && splits > cfg.tail_splits) splits = cfg.tail_splits;
+    if (splits < 2) return t;
+    t.full_tiles = tiles - rest;
+    t.tail_tiles = rest;
+    t.splits = int(splits);
+    t.bytes = size_t(rest) * size_t(tile_m) * size_t(cfg.block_n) * 4;
+    return t;
+}
+
 // lda / ldb / ldc: row pitch in elements of A (M x K), B (N x K) and C (M x N); 0 = dense.
 static int gemm_launch(tesserae_gemm_plan* p, const void* a, int64_t lda, const void* b, int64_t ldb, void* c, int64_t ldc,
                        const tesserae_gemm_scales* scales, const void* bias,
-                       float alpha, int64_t m, int64_t n, int64_t k, void* stream) {
+                       float alpha, int64_t m, int64_t n, int64_t k, void* stream,
+                       void* tail_ws = nullptr, size_t tail_ws_bytes = 0) {
     if (!p || !a || !b || !c) return fail("gemm_run: null argument");
     if (int drc = check_plan_device(p, "gemm_run")) return drc;
     if (m <= 0 || n <= 0 || k <= 0) return fail("gemm_run: M, N and K must be positive");
     if (m > INT32_MAX || n > INT32_MAX || k > INT32_MAX) return fail("gemm_run: dimension exceeds 2^31-1");
     const KernelConfig& cfg = p->cfg;
     if (cfg.scatter) return fail("gemm_run: this plan stores row-scattered output; use tesserae_gemm_ksplit_scatter");
+    if (cfg.grouped) return fail("gemm_run: this plan walks a problem table; use tesserae_gemm_run_grouped");
     if (cfg.has_bias && !bias) return fail("gemm_run: this kernel was built with a bias but none was given");
     if (cfg.has_bias && (reinterpret_cast<uintptr_t>(bias) & 15u)) return fail("gemm_run: bias must be 16-byte aligned");
     const bool scaled = cfg.scale_mode != TESSERAE_SCALE_NONE;
@@ -447,11 +491,37 @@ static int gemm_launch(tesserae_gemm_plan* p, const void* a, int64_t lda, const 
         return tesserae_launch_kernel_ex(p->function, grid, block, cluster, cfg.smem_bytes, stream, args, 12);
     }
     if (cfg.scale_mode == TESSERAE_SCALE_FP8_BLOCK) {
+        // Stream-K tail: with a workspace, the tiles past the last whole wave are split into ranges of K blocks.
+        TailPlan tp = plan_tail(p, m, n, k);
+        alignas(64) unsigned char tm_ws[128];
+        if (tp.tail_tiles > 0 && tail_ws) {
+            if (tail_ws_bytes < tp.bytes) return fail("gemm_run: tail workspace too small, need " + std::to_string(tp.bytes) + " bytes");
+            if (reinterpret_cast<uintptr_t>(tail_ws) & 127u) return fail("gemm_run: tail workspace must be 128-byte aligned");
+            rc = tesserae_tensor_map_2d(tm_ws, TESSERAE_F32, tail_ws, uint64_t(cfg.block_n), uint64_t(tp.tail_tiles) * tile_m,
+                                        uint64_t(cfg.block_n) * 4, 32, 32, kStoreSwizzleB);
+            if (rc != 0) return rc;
+        } else {
+            tp = TailPlan{};
+            tp.full_tiles = tiles;
+            memcpy(tm_ws, tm_c, 128);                     // never read: every tile is computed whole
+        }
+        const int64_t units = tp.full_tiles + tp.tail_tiles * tp.splits;
+        const int uclusters = int(units < p->max_clusters ? units : p->max_clusters);
+        const int ugrid[3] = {uclusters * cfg.cta_group, 1, 1};
+        const int full_i = int(tp.full_tiles), splits_i = tp.splits;
         const tesserae_launch_arg args[] = {
-            {tm_a, 128}, {tm_b, 128}, {tm_c, 128}, {&scales->scale_a, sizeof(void*)}, {&scales->scale_b, sizeof(void*)},
+            {tm_a, 128}, {tm_b, 128}, {tm_c, 128}, {tm_ws, 128}, {&scales->scale_a, sizeof(void*)}, {&scales->scale_b, sizeof(void*)},
             {&bias, sizeof(void*)}, {&alpha, sizeof(float)}, {&mi, sizeof(int)}, {&ni, sizeof(int)}, {&ki, sizeof(int)},
-            {&gmi, sizeof(int)}, {&p->d_status, sizeof(void*)}};
-        return tesserae_launch_kernel_ex(p->function, grid, block, cluster, cfg.smem_bytes, stream, args, 12);
+            {&gmi, sizeof(int)}, {&full_i, sizeof(int)}, {&splits_i, sizeof(int)}, {&p->d_status, sizeof(void*)}};
+        rc = tesserae_launch_kernel_ex(p->function, ugrid, block, cluster, cfg.smem_bytes, stream, args, 15);
+        if (rc != 0 || tp.tail_tiles == 0) return rc;
+        const int tgrid[3] = {int(tp.tail_tiles), 8, 1};
+        const int tblock[3] = {256, 1, 1};
+        const int one[3] = {1, 1, 1};
+        const long long ldc_ll = ldc;
+        const tesserae_launch_arg targs[] = {{&tail_ws, sizeof(void*)}, {&c, sizeof(void*)}, {&bias, sizeof(void*)}, {&mi, sizeof(int)},
+                                             {&ni, sizeof(int)}, {&ldc_ll, sizeof(long long)}, {&gmi, sizeof(int)}, {&full_i, sizeof(int)}};
+        return tesserae_launch_kernel_ex(p->tail_function, tgrid, tblock, one, 0, stream, targs, 8);
     }
     const tesserae_launch_arg args[] = {
         {tm_a, 128}, {tm_b, 128}, {tm_c, 128}, {&bias, sizeof(void*)}, {&alpha, sizeof(float)},
@@ -465,9 +535,109 @@ int tesserae_gemm_run_scaled(tesserae_gemm_plan* p, const void* a, const void* b
     return gemm_launch(p, a, 0, b, 0, c, 0, scales, bias, alpha, m, n, k, stream);
 }
 
+size_t tesserae_gemm_tail_workspace_bytes(const tesserae_gemm_plan* p, int64_t m, int64_t n, int64_t k) {
+    if (!p || m <= 0 || n <= 0 || k <= 0) return 0;
+    return plan_tail(p, m, n, k).bytes;
+}
+
+int tesserae_gemm_run_scaled_ws(tesserae_gemm_plan* p, const void* a, const void* b, void* c,
+                                const tesserae_gemm_scales* scales, const void* bias,
+                                float alpha, int64_t m, int64_t n, int64_t k,
+                                void* workspace, size_t workspace_bytes, void* stream) {
+    return gemm_launch(p, a, 0, b, 0, c, 0, scales, bias, alpha, m, n, k, stream, workspace, workspace_bytes);
+}
+
 int tesserae_gemm_run(tesserae_gemm_plan* p, const void* a, const void* b, void* c, const void* bias,
                       float alpha, int64_t m, int64_t n, int64_t k, void* stream) {
     return gemm_launch(p, a, 0, b, 0, c, 0, nullptr, bias, alpha, m, n, k, stream);
+}
+
+// ------------------------------------------------------------------ grouped
+namespace {
+// Row of the problem table as the kernel reads it (TsGroupedProblem in gemm_sm100_dense.cuh).
+struct alignas(64) GroupedRow {
+    unsigned char a[128], b[128], c[128];
+    const void* bias;
+    int M, N, K;
+    int tile_start, num_m, num_n, group_m;
+    int pad[7];
+};
+static_assert(sizeof(GroupedRow) == 448, "the problem table's row is 448 bytes on both sides");
+}  // namespace
+
+size_t tesserae_gemm_grouped_workspace_bytes(int n_problems) {
+    return n_problems < 1 ? 0 : size_t(n_problems + 1) * sizeof(GroupedRow);
+}
+
+int tesserae_gemm_run_grouped(tesserae_gemm_plan* p, const tesserae_gemm_problem* problems, int n_problems, float alpha,
+                              void* workspace, size_t workspace_bytes, void* stream) {
+    if (!p || !problems || !workspace) return fail("gemm_run_grouped: null argument");
+    if (int drc = check_plan_device(p, "gemm_run_grouped")) return drc;
+    const KernelConfig& cfg = p->cfg;
+    if (!cfg.grouped) return fail("gemm_run_grouped: the plan's spec must have grouped = 1");
+    if (n_problems < 1 || n_problems > 65536) return fail("gemm_run_grouped: n_problems must be in 1..65536");
+    const size_t need = tesserae_gemm_grouped_workspace_bytes(n_problems);
+    if (workspace_bytes < need) return fail("gemm_run_grouped: workspace too small, need " + std::to_string(need) + " bytes");
+    if (reinterpret_cast<uintptr_t>(workspace) & 63u) return fail("gemm_run_grouped: workspace must be 64-byte aligned");
+    cudaError_t e = cudaSuccess;
+    if (p->h_table_cap < need) {
+        if (p->h_table) { if (p->ev_table) cudaEventSynchronize(p->ev_table); cudaFreeHost(p->h_table); p->h_table = nullptr; p->h_table_cap = 0; }
+        e = cudaHostAlloc(&p->h_table, need, cudaHostAllocDefault);
+        if (e != cudaSuccess) return fail(std::string("gemm_run_grouped: ") + cudaGetErrorString(e));
+        p->h_table_cap = need;
+    }
+    if (!p->ev_table) {
+        e = cudaEventCreateWithFlags(&p->ev_table, cudaEventDisableTiming);
+        if (e != cudaSuccess) return fail(std::string("gemm_run_grouped: ") + cudaGetErrorString(e));
+    } else {
+        cudaEventSynchronize(p->ev_table);       // the previous call's copy has left the pinned table
+    }
+    const int ebits = tesserae::spec::elem_bits(cfg.elem);
+    const int ob = out_bytes(cfg.out_elem);
+    const int op_swizzle = cfg.desc.swizzle.b;
+    const int64_t tile_m = 128 * cfg.cta_group;
+    GroupedRow* rows = static_cast<GroupedRow*>(p->h_table);
+    memset(rows, 0, need);
+    int64_t tiles = 0;
+    for (int i = 0; i < n_problems; ++i) {
+        const tesserae_gemm_problem& q = problems[i];
+        const std::string at = "gemm_run_grouped: problem " + std::to_string(i) + ": ";
+        if (!q.a || !q.b || !q.c) return fail(at + "null operand");
+        if (q.m <= 0 || q.n <= 0 || q.k <= 0 || q.m > INT32_MAX || q.n > INT32_MAX || q.k > INT32_MAX) return fail(at + "bad dimensions");
+        if ((q.k * ebits / 8) % 16 != 0) return fail(at + "K * element size must be a multiple of 16 bytes");
+        if ((q.n * ob) % 16 != 0) return fail(at + "N * output element size must be a multiple of 16 bytes");
+        if (cfg.has_bias && !q.bias) return fail(at + "this kernel was built with a bias but none was given");
+        if (cfg.has_bias && (reinterpret_cast<uintptr_t>(q.bias) & 15u)) return fail(at + "bias must be 16-byte aligned");
+        GroupedRow& r = rows[i];
+        const uint64_t row_bytes = uint64_t(q.k) * ebits / 8;
+        int rc = tesserae_tensor_map_2d(r.a, cfg.elem, q.a, uint64_t(q.k), uint64_t(q.m), row_bytes, uint32_t(cfg.block_k), 128, op_swizzle);
+        if (rc == 0) rc = tesserae_tensor_map_2d(r.b, cfg.elem, q.b, uint64_t(q.k), uint64_t(q.n), row_bytes, uint32_t(cfg.block_k),
+                                                 uint32_t(cfg.b_box_rows), op_swizzle);
+        if (rc == 0) rc = tesserae_tensor_map_2d(r.c, cfg.out_elem, q.c, uint64_t(q.n), uint64_t(q.m), uint64_t(q.n) * ob,
+                                                 uint32_t(128 / ob), 32, kStoreSwizzleB);
+        if (rc != 0) return rc;
+        r.bias = q.bias;
+        r.M = int(q.m); r.N = int(q.n); r.K = int(q.k);
+        r.num_m = int((q.m + tile_m - 1) / tile_m);
+        r.num_n = int((q.n + cfg.block_n - 1) / cfg.block_n);
+        r.group_m = pick_group_m(cfg, q.m, q.k);
+        r.tile_start = int(tiles);
+        tiles += int64_t(r.num_m) * r.num_n;
+        if (tiles > INT32_MAX) return fail("gemm_run_grouped: too many tiles");
+    }
+    rows[n_problems].tile_start = int(tiles);            // the sentinel row the tile search stops at
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    e = cudaMemcpyAsync(workspace, rows, need, cudaMemcpyHostToDevice, st);
+    if (e == cudaSuccess) e = cudaEventRecord(p->ev_table, st);
+    if (e != cudaSuccess) return fail(std::string("gemm_run_grouped: ") + cudaGetErrorString(e));
+    const int clusters = int(tiles < p->max_clusters ? tiles : p->max_clusters);
+    const int grid[3] = {clusters * cfg.cta_group, 1, 1};
+    const int block[3] = {cfg.threads, 1, 1};
+    const int cluster[3] = {cfg.cta_group, 1, 1};
+    const int total = int(tiles);
+    const tesserae_launch_arg args[] = {{&workspace, sizeof(void*)}, {&total, sizeof(int)}, {&alpha, sizeof(float)},
+                                        {&p->d_status, sizeof(void*)}};
+    return tesserae_launch_kernel_ex(p->function, grid, block, cluster, cfg.smem_bytes, stream, args, 4);
 }
 
 // ------------------------------------------------------------------ K-split

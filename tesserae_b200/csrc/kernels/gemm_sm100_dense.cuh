@@ -45,7 +45,28 @@
 //                    the same schedule would all send to the same owner at the same time (the rows of the first
 //                    raster group) and queue up on that owner's NVLink ingress; with a different rotation per
 //                    source GPU the owners are visited round robin.
+//   TS_GROUPED       0/1: grouped GEMM.  One launch walks the tiles of a list of independent problems (each with its
+//                    own A, B, C, bias, M, N, K): the problems' tensor maps and sizes sit in a table in global
+//                    memory (TsGroupedProblem, written by the host before the launch), global tile t belongs to the
+//                    problem whose [tile_start, next tile_start) holds it, and every role looks its problem up as
+//                    it moves from tile to tile.  Tiles of different problems fill one wave together, so a list of
+//                    small problems is not quantised problem by problem.
 #pragma once
+
+#ifndef TS_GROUPED
+#define TS_GROUPED 0
+#endif
+#if TS_GROUPED
+// One row of the problem table; the table has n + 1 rows, the last one holding only tile_start = total tiles.
+struct __align__(64) TsGroupedProblem {
+    TsTensorMap a, b, c;
+    const ts_u16* bias;
+    int M, N, K;
+    int tile_start, num_m, num_n, group_m;
+    int pad[7];
+};
+static_assert(sizeof(TsGroupedProblem) == 448, "host and device must agree on the problem table's row");
+#endif
 
 #ifndef TS_SCATTER
 #define TS_SCATTER 0
@@ -94,9 +115,35 @@ static_assert(kBlockN % kChunkCols == 0, "TS_BLOCK_N must be a multiple of the s
 static_assert(kNumAcc * kBlockN <= 512, "accumulators exceed tensor memory");
 static_assert(kSmemTotal + 1024 <= 232448, "shared memory over the 227 KB limit");
 
+// What a role needs to know about the tile it is on.
+struct TileInfo {
+    ts_u32 local_tile, num_m, num_n, num_k_blocks, group_m;
+    int M, N;
+    const TsTensorMap *a, *b, *c;
+    const ts_u16* bias;
+};
+#if TS_GROUPED
+// `cursor` is the problem the previous tile of this role belonged to; tiles only move forward.
+TS_DEV TileInfo tile_info(const TsGroupedProblem* probs, ts_u32 t, ts_u32& cursor) {
+    while (t >= (ts_u32)__ldg(&probs[cursor + 1].tile_start)) ++cursor;
+    const TsGroupedProblem* pr = probs + cursor;
+    TileInfo ti;
+    ti.local_tile = t - (ts_u32)__ldg(&pr->tile_start);
+    ti.num_m = (ts_u32)__ldg(&pr->num_m); ti.num_n = (ts_u32)__ldg(&pr->num_n); ti.group_m = (ts_u32)__ldg(&pr->group_m);
+    ti.M = __ldg(&pr->M); ti.N = __ldg(&pr->N);
+    ti.num_k_blocks = ((ts_u32)__ldg(&pr->K) + kBlockK - 1) / kBlockK;
+    ti.a = &pr->a; ti.b = &pr->b; ti.c = &pr->c;
+    ti.bias = reinterpret_cast<const ts_u16*>(__ldg(reinterpret_cast<const ts_u64*>(&pr->bias)));
+    return ti;
+}
+#endif
+
 }  // namespace ts_dense
 
 extern "C" __global__ void __launch_bounds__(192, 1)
+#if TS_GROUPED
+TS_KERNEL_NAME(const TsGroupedProblem* __restrict__ probs, int total_tiles, float alpha, ts_u32* __restrict__ status)
+#else
 TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
                const __grid_constant__ TsTensorMap tmap_b,
 #if TS_SCATTER
@@ -107,6 +154,7 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
                const ts_u16* __restrict__ bias,
                float alpha, int M, int N, int K, int group_m,
                ts_u32* __restrict__ status)
+#endif
 {
     using namespace ts_dense;
     extern __shared__ ts_u8 ts_smem_raw[];
@@ -127,20 +175,35 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
     const ts_u32 cta_rank = (TS_CTA_GROUP == 2) ? ts_cluster_ctarank() : 0u;
     const bool   is_leader = (cta_rank == 0);
 
+#if TS_GROUPED
+    const ts_u32 num_tiles = (ts_u32)total_tiles;
+#else
     const ts_u32 num_m = ((ts_u32)M + kTileM - 1) / kTileM;
     const ts_u32 num_n = ((ts_u32)N + kBlockN - 1) / kBlockN;
     const ts_u32 num_tiles = num_m * num_n;
     const ts_u32 num_k_blocks = ((ts_u32)K + kBlockK - 1) / kBlockK;
+    // the one problem of an ordinary launch, in the form the tile loops read
+    TileInfo ti;
+    ti.num_m = num_m; ti.num_n = num_n; ti.num_k_blocks = num_k_blocks; ti.group_m = (ts_u32)group_m;
+    ti.M = M; ti.N = N; ti.a = &tmap_a; ti.b = &tmap_b; ti.bias = bias;
+#if TS_SCATTER
+    ti.c = &tmap_cs.m[0];
+#else
+    ti.c = &tmap_c;
+#endif
+#endif
     const ts_u32 first_tile = (TS_CTA_GROUP == 2) ? ts_cluster_id_x() : blockIdx.x;
     const ts_u32 tile_step  = (TS_CTA_GROUP == 2) ? ts_nclusters_x() : gridDim.x;
 
     if (warp_id == 0 && lane == 0) {
+#if !TS_GROUPED
         ts_prefetch_tmap(&tmap_a);
         ts_prefetch_tmap(&tmap_b);
 #if TS_SCATTER
         for (int g = 0; g * rows_per_owner < M && g < 8; ++g) ts_prefetch_tmap(&tmap_cs.m[g]);
 #else
         ts_prefetch_tmap(&tmap_c);
+#endif
 #endif
         for (ts_u32 s = 0; s < kStages; ++s) {
             ts_mbar_init(full_bar + 8 * s, 1);    // producer's arrive.expect_tx (leader CTA)
@@ -169,15 +232,24 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
             // In a pair, every byte count is signalled on the leader CTA's full barrier.
             ts_u32 it = 0;
             bool ok = true;
+#if TS_GROUPED
+            ts_u32 cursor = 0;
+#endif
             for (ts_u32 t = first_tile; t < num_tiles && ok; t += tile_step) {
+#if TS_GROUPED
+                const TileInfo ti = tile_info(probs, t, cursor);
+                const ts_u32 lt = ti.local_tile;
+#else
+                const ts_u32 lt = t;
+#endif
                 ts_u32 m_blk, n_blk;
-                ts_decode_tile(t, num_m, num_n, (ts_u32)group_m, m_blk, n_blk);
+                ts_decode_tile(lt, ti.num_m, ti.num_n, ti.group_m, m_blk, n_blk);
 #if TS_SCATTER
                 m_blk = (m_blk + (ts_u32)m_rotate) % num_m;
 #endif
                 const int a_row = (int)(m_blk * kTileM + cta_rank * kBlockM);
                 const int b_row = (int)(n_blk * kBlockN + cta_rank * kLoadN);
-                for (ts_u32 kb = 0; kb < num_k_blocks; ++kb, ++it) {
+                for (ts_u32 kb = 0; kb < ti.num_k_blocks; ++kb, ++it) {
                     const ts_u32 s = it % kStages;
                     const ts_u32 ph = (it / kStages) & 1u;
                     if (!ts_mbar_wait(empty_bar + 8 * s, ph ^ 1u)) {
@@ -186,13 +258,13 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
                     const int kc = (int)(kb * kBlockK);
                     if (TS_CTA_GROUP == 1) {
                         ts_mbar_arrive_expect_tx(full_bar + 8 * s, kStageBytes);
-                        ts_tma_load_2d(smem_a + s * kSmemA, &tmap_a, full_bar + 8 * s, kc, a_row);
-                        ts_tma_load_2d(smem_b + s * kSmemB, &tmap_b, full_bar + 8 * s, kc, b_row);
+                        ts_tma_load_2d(smem_a + s * kSmemA, ti.a, full_bar + 8 * s, kc, a_row);
+                        ts_tma_load_2d(smem_b + s * kSmemB, ti.b, full_bar + 8 * s, kc, b_row);
                     } else {
                         const ts_u32 leader_full = ts_mapa(full_bar + 8 * s, 0);
                         if (is_leader) ts_mbar_arrive_expect_tx(full_bar + 8 * s, kStageBytes * 2);
-                        ts_tma_load_2d_pair(smem_a + s * kSmemA, &tmap_a, leader_full, kc, a_row);
-                        ts_tma_load_2d_pair(smem_b + s * kSmemB, &tmap_b, leader_full, kc, b_row);
+                        ts_tma_load_2d_pair(smem_a + s * kSmemA, ti.a, leader_full, kc, a_row);
+                        ts_tma_load_2d_pair(smem_b + s * kSmemB, ti.b, leader_full, kc, b_row);
                     }
                 }
             }
@@ -206,7 +278,13 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
             const bool elected = ts_elect_one();
             ts_u32 it = 0, tile_iter = 0;
             bool ok = true;
+#if TS_GROUPED
+            ts_u32 cursor = 0;
+#endif
             for (ts_u32 t = first_tile; t < num_tiles && ok; t += tile_step, ++tile_iter) {
+#if TS_GROUPED
+                const TileInfo ti = tile_info(probs, t, cursor);
+#endif
                 const ts_u32 acc = tile_iter % kNumAcc;
                 const ts_u32 acc_ph = (tile_iter / kNumAcc) & 1u;
                 if (!ts_mbar_wait(tmem_empty_bar + 8 * acc, acc_ph ^ 1u)) {
@@ -215,7 +293,7 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
                 }
                 ts_tc_fence_after();
                 const ts_u32 d_tmem = tmem_base + acc * kBlockN;
-                for (ts_u32 kb = 0; kb < num_k_blocks; ++kb, ++it) {
+                for (ts_u32 kb = 0; kb < ti.num_k_blocks; ++kb, ++it) {
                     const ts_u32 s = it % kStages;
                     const ts_u32 ph = (it / kStages) & 1u;
                     if (!ts_mbar_wait(full_bar + 8 * s, ph)) {
@@ -255,9 +333,20 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
         const ts_u32 leader_tmem_empty = (TS_CTA_GROUP == 2) ? ts_mapa(tmem_empty_bar, 0) : tmem_empty_bar;
         ts_u32 tile_iter = 0, chunk_iter = 0;
         bool ok = true;
+#if TS_GROUPED
+        ts_u32 cursor = 0;
+#endif
         for (ts_u32 t = first_tile; t < num_tiles && ok; t += tile_step, ++tile_iter) {
+#if TS_GROUPED
+            const TileInfo ti = tile_info(probs, t, cursor);
+            const ts_u32 lt = ti.local_tile;
+#else
+            const ts_u32 lt = t;
+#endif
+            const int M = ti.M, N = ti.N;                      // (shadow the launch arguments: per problem when grouped)
+            const ts_u16* const bias = ti.bias;
             ts_u32 m_blk, n_blk;
-            ts_decode_tile(t, num_m, num_n, (ts_u32)group_m, m_blk, n_blk);
+            ts_decode_tile(lt, ti.num_m, ti.num_n, ti.group_m, m_blk, n_blk);
 #if TS_SCATTER
             m_blk = (m_blk + (ts_u32)m_rotate) % num_m;
 #endif
@@ -335,7 +424,7 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
 #endif
                     }
 #else
-                    if (col0 < (ts_u32)N && row0 < M) ts_tma_store_2d(&tmap_c, buf, (int)col0, row0);
+                    if (col0 < (ts_u32)N && row0 < M) ts_tma_store_2d(ti.c, buf, (int)col0, row0);
 #endif
                     ts_bulk_commit();   // committed even when empty so that "one group pending" always means the previous chunk
                 }

@@ -27,6 +27,14 @@
 //    32 K blocks handed out by shuffle (sB); a buffer is released as soon as its last load
 //    has landed; the epilogue fills all staging buffers of the warp before one fence and commit.
 //
+//  - Stream-K tail.  The host may name the last `num_tiles - full_tiles` tiles of the raster order as tail tiles
+//    and split each into `tail_splits` ranges of K blocks; every (tile, range) is then a unit of work of its own,
+//    dealt to the CTAs like a whole tile.  A tail unit adds its fp32 partial into a workspace tile with TMA
+//    reduce-adds (no bias, no cast); the small kernel at the end of this file adds the bias, casts into C and
+//    clears the workspace.  With a tile count a little over a whole number of waves this replaces a last wave
+//    of a few tiles, one whole K loop long, by a wave of K-range units a fraction as long.  The order of the
+//    additions into the workspace is not fixed, so tail tiles are not bit-reproducible from run to run.
+//
 // Compile-time configuration (macros): TS_KERNEL_NAME, TS_CTA_GROUP (1|2), TS_BLOCK_N (128|256),
 // TS_STAGES, TS_PROMO_WARPS (8|16), TS_OUT_F32, TS_HAS_BIAS, TS_FP8_SPLIT.
 #pragma once
@@ -69,9 +77,6 @@ constexpr ts_u32 kThreads     = 32 * (kFirstPromoWarp + kNumPromoWarps);
 constexpr int    kRegsIssue   = kNumPromoWarps == 8 ? 40 : 32;  // register budgets after the split (per thread)
 constexpr int    kRegsPromo   = kNumPromoWarps == 8 ? 232 : 112;
 constexpr ts_u32 kLdCols      = kNumPromoWarps == 8 ? 32 : 16;  // TMEM columns per load of the promotion loop
-#ifndef TS_SCALES_EARLY
-#define TS_SCALES_EARLY 1
-#endif
 #ifndef TS_SCALE_RING
 #define TS_SCALE_RING 2
 #endif
@@ -84,6 +89,24 @@ static_assert(kBlockN == 128 || kBlockN == 256, "TS_BLOCK_N must be 128 or 256 (
 static_assert(kWarpCols % kChunkCols == 0 && kWarpCols % 32 == 0, "store chunk must divide a warp's column range");
 static_assert(kSmemTotal + 1024 <= 232448, "shared memory over the 227 KB limit");
 
+// One unit of work: a tile and a range of its K blocks.  `range` packs first block | blocks << 16 (K < 2^23);
+// `ws_row` is the unit's first workspace row, or kNoTail for a whole tile.
+constexpr ts_u32 kNoTail = 0xffffffffu;
+TS_DEV void unit_of(ts_u32 u, ts_u32 full_tiles, ts_u32 splits, ts_u32 num_k_blocks, ts_u32& tile, ts_u32& range, ts_u32& ws_row) {
+    if (u < full_tiles) { tile = u; range = num_k_blocks << 16; ws_row = kNoTail; return; }
+    const ts_u32 v = u - full_tiles, ti = v / splits, part = v - ti * splits;
+    const ts_u32 kb0 = part * num_k_blocks / splits;
+    tile = full_tiles + ti;
+    range = kb0 | (((part + 1) * num_k_blocks / splits - kb0) << 16);
+    ws_row = ti * kTileM;
+}
+// The same for a role that only needs the unit's number of K blocks.
+TS_DEV ts_u32 unit_blocks_of(ts_u32 u, ts_u32 full_tiles, ts_u32 splits, ts_u32 num_k_blocks) {
+    if (u < full_tiles) return num_k_blocks;
+    const ts_u32 part = (u - full_tiles) % splits;
+    return (part + 1) * num_k_blocks / splits - part * num_k_blocks / splits;
+}
+
 TS_DEV void ts_tmem_ld(ts_u32 taddr, ts_u32 (&r)[16]) { ts_tmem_ld_32x32b_x16(taddr, r); }
 TS_DEV void ts_tmem_ld(ts_u32 taddr, ts_u32 (&r)[32]) { ts_tmem_ld_32x32b_x32(taddr, r); }
 
@@ -93,10 +116,12 @@ extern "C" __global__ void __launch_bounds__(128 + 32 * TS_PROMO_WARPS, 1)
 TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
                const __grid_constant__ TsTensorMap tmap_b,
                const __grid_constant__ TsTensorMap tmap_c,
+               const __grid_constant__ TsTensorMap tmap_ws,   // fp32 [tail tiles * tile rows][BLOCK_N]: the tail units' sums
                const float* __restrict__ scale_a,      // [M][K/128]
                const float* __restrict__ scale_b,      // [ceil(N/128)][K/128]
                const ts_u16* __restrict__ bias,
                float alpha, int M, int N, int K, int group_m,
+               int full_tiles_arg, int tail_splits_arg,  // tiles computed whole; K ranges per remaining (tail) tile
                ts_u32* __restrict__ status)
 {
     using namespace ts_fp8;
@@ -121,6 +146,11 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
     const ts_u32 num_n = ((ts_u32)N + kBlockN - 1) / kBlockN;
     const ts_u32 num_tiles = num_m * num_n;
     const ts_u32 num_k_blocks = ((ts_u32)K + kBlockK - 1) / kBlockK;
+    // (the host passes full_tiles <= tiles and 1 <= tail_splits <= K blocks; used as they come, so that they can be
+    // re-read from the parameter bank instead of being held in registers across the promotion loop)
+    const ts_u32 full_tiles = (ts_u32)full_tiles_arg;
+    const ts_u32 splits = (ts_u32)tail_splits_arg;
+    const ts_u32 num_units = full_tiles + (num_tiles - full_tiles) * splits;
     const ts_u32 first_tile = (TS_CTA_GROUP == 2) ? ts_cluster_id_x() : blockIdx.x;
     const ts_u32 tile_step  = (TS_CTA_GROUP == 2) ? ts_nclusters_x() : gridDim.x;
 
@@ -128,6 +158,7 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
         ts_prefetch_tmap(&tmap_a);
         ts_prefetch_tmap(&tmap_b);
         ts_prefetch_tmap(&tmap_c);
+        if (full_tiles < num_tiles) ts_prefetch_tmap(&tmap_ws);
         for (ts_u32 s = 0; s < kStages; ++s) {
             ts_mbar_init(full_bar + 8 * s, 1);
             ts_mbar_init(empty_bar + 8 * s, kHalves);          // one commit per issuing warp
@@ -159,12 +190,19 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
         if (lane == 0) {
             ts_u32 it = 0;
             bool ok = true;
-            for (ts_u32 t = first_tile; t < num_tiles && ok; t += tile_step) {
+            for (ts_u32 u = first_tile; u < num_units && ok; u += tile_step) {
+                ts_u32 tile = u, kb_begin = 0, kb_end = num_k_blocks;
+                if (u >= full_tiles) {
+                    const ts_u32 v = u - full_tiles, ti = v / splits, part = v - ti * splits;
+                    tile = full_tiles + ti;
+                    kb_begin = part * num_k_blocks / splits;
+                    kb_end = (part + 1) * num_k_blocks / splits;
+                }
                 ts_u32 m_blk, n_blk;
-                ts_decode_tile(t, num_m, num_n, (ts_u32)group_m, m_blk, n_blk);
+                ts_decode_tile(tile, num_m, num_n, (ts_u32)group_m, m_blk, n_blk);
                 const int a_row = (int)(m_blk * kTileM + cta_rank * kBlockM);
                 const int b_row = (int)(n_blk * kBlockN + cta_rank * kLoadN);
-                for (ts_u32 kb = 0; kb < num_k_blocks; ++kb, ++it) {
+                for (ts_u32 kb = kb_begin; kb < kb_end; ++kb, ++it) {
                     const ts_u32 s = it % kStages;
                     const ts_u32 ph = (it / kStages) & 1u;
                     if (!ts_mbar_wait(empty_bar + 8 * s, ph ^ 1u)) {
@@ -202,8 +240,9 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
             const bool elected = ts_elect_one();
             ts_u32 it = 0;     // k-block counter across tiles: selects the smem stage and, with h, the TMEM buffer
             bool ok = true;
-            for (ts_u32 t = first_tile; t < num_tiles && ok; t += tile_step) {
-                for (ts_u32 kb = 0; kb < num_k_blocks; ++kb, ++it) {
+            for (ts_u32 u = first_tile; u < num_units && ok; u += tile_step) {
+                const ts_u32 unit_blocks = unit_blocks_of(u, full_tiles, splits, num_k_blocks);
+                for (ts_u32 kb = 0; kb < unit_blocks; ++kb, ++it) {
                     const ts_u32 s = it % kStages;
                     const ts_u32 ph = (it / kStages) & 1u;
                     const ts_u32 unit = it * kHalves + h;
@@ -248,7 +287,7 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
         const ts_u32 store_smem = smem_c + (warp_id - kFirstPromoWarp) * kStoreBufs * kStoreBuf;
         const ts_u32 row_sw = (lane & 7u) << 4;
         const ts_u32 leader_tmem_empty = (TS_CTA_GROUP == 2) ? ts_mapa(tmem_empty_bar, 0) : tmem_empty_bar;
-        const ts_u32 nkb = num_k_blocks;
+        const ts_u32 nkb_all = num_k_blocks;
         const ts_u32 n_scale_rows = ((ts_u32)N + 127u) / 128u;
         ts_u32 it = 0;
         bool ok = true;
@@ -261,41 +300,43 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
         const float* sb_ptr;
         float sa_r[kScaleRing];
         float sb_l;
-        auto scales_of_tile = [&](ts_u32 mb, ts_u32 nb) __attribute__((always_inline)) {
+        // (kb0, nkb: the unit's range of K blocks; the pointers are moved to its first block)
+        auto scales_of_tile = [&](ts_u32 mb, ts_u32 nb, ts_u32 kb0, ts_u32 nkb) __attribute__((always_inline)) {
             const ts_u32 r = mb * kTileM + cta_rank * kBlockM + quarter * 32 + lane;
             ts_u32 sb_row = (nb * kBlockN + half * kWarpCols) / 128u;
             if (sb_row >= n_scale_rows) sb_row = n_scale_rows - 1;
-            sa_ptr = scale_a + (size_t)(r < (ts_u32)M ? r : 0u) * nkb;
-            sb_ptr = scale_b + (size_t)sb_row * nkb;
+            sa_ptr = scale_a + (size_t)(r < (ts_u32)M ? r : 0u) * nkb_all + kb0;
+            sb_ptr = scale_b + (size_t)sb_row * nkb_all + kb0;
             // (predicated loads, not selects: a select on the loaded value would wait for it here)
 #pragma unroll
             for (ts_u32 j = 0; j < kScaleRing; ++j) { sa_r[j] = 0.f; if (j < nkb) sa_r[j] = __ldg(sa_ptr + j); }
             sb_l = 0.f;
             if (lane < nkb) sb_l = __ldg(sb_ptr + lane);
         };
-        auto prefetch_scales = [&](ts_u32 mb, ts_u32 nb) __attribute__((always_inline)) {
-            const ts_u32 r = mb * kTileM + cta_rank * kBlockM + quarter * 32 + lane;
-            ts_u32 sb_row = (nb * kBlockN + half * kWarpCols) / 128u;
-            if (sb_row >= n_scale_rows) sb_row = n_scale_rows - 1;
-            asm volatile("prefetch.global.L1 [%0];" :: "l"(scale_a + (size_t)(r < (ts_u32)M ? r : 0u) * nkb));
-            if (lane == 0) asm volatile("prefetch.global.L1 [%0];" :: "l"(scale_b + (size_t)sb_row * nkb));
-        };
         // Tile coordinates are decoded once per tile, one tile ahead (three integer divisions each: at the top of a
         // tile they run behind the first wait, at its end they would sit in front of the next tile's first load).
         ts_u32 m_blk = 0, n_blk = 0;
         const bool fast_decode = num_tiles < (1u << 22);
         const float inv_group = 1.0f / (float)((ts_u32)group_m * num_n), inv_gm = 1.0f / (float)group_m;
-        if (first_tile < num_tiles) {
-            ts_decode_tile(first_tile, num_m, num_n, (ts_u32)group_m, m_blk, n_blk);
-            scales_of_tile(m_blk, n_blk);
+        ts_u32 un_range = 0, un_ws = kNoTail;
+        if (first_tile < num_units) {
+            ts_u32 tile;
+            unit_of(first_tile, full_tiles, splits, num_k_blocks, tile, un_range, un_ws);
+            ts_decode_tile(tile, num_m, num_n, (ts_u32)group_m, m_blk, n_blk);
+            scales_of_tile(m_blk, n_blk, un_range & 0xffffu, un_range >> 16);
         }
-        for (ts_u32 t = first_tile; t < num_tiles && ok; t += tile_step) {
-            const bool has_next = t + tile_step < num_tiles;
+        for (ts_u32 u = first_tile; u < num_units && ok; u += tile_step) {
+            const bool has_next = u + tile_step < num_units;
             ts_u32 m_next = 0, n_next = 0;
             if (has_next) {
-                if (fast_decode) ts_decode_tile_fast(t + tile_step, num_m, num_n, (ts_u32)group_m, inv_group, inv_gm, m_next, n_next);
-                else             ts_decode_tile(t + tile_step, num_m, num_n, (ts_u32)group_m, m_next, n_next);
+                // (the tile index of the next unit is one compare for a whole tile and a division for a tail unit; its
+                // range of K blocks is worked out after this unit's K loop, so that nothing more stays live across it)
+                const ts_u32 un = u + tile_step;
+                const ts_u32 tile = un < full_tiles ? un : full_tiles + (un - full_tiles) / splits;
+                if (fast_decode) ts_decode_tile_fast(tile, num_m, num_n, (ts_u32)group_m, inv_group, inv_gm, m_next, n_next);
+                else             ts_decode_tile(tile, num_m, num_n, (ts_u32)group_m, m_next, n_next);
             }
+            const ts_u32 nkb = un_range >> 16;
             const ts_u32 col_base = n_blk * kBlockN + half * kWarpCols;
             // 128 x BLOCK_N fp32 accumulators of the tile, one row per lane, held as packed pairs: the multiply-adds
             // are issued two at a time (fma.rn.f32x2: the same two roundings as two scalar fmas, half the issue slots).
@@ -378,13 +419,47 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
             if (!ok) break;
             // The next tile's first scales: ask for the lines now (no register is tied up while the accumulators
             // are still live), load them after the epilogue.
-#if TS_SCALES_EARLY
-            if (has_next) scales_of_tile(m_next, n_next);
-#else
-            if (has_next) prefetch_scales(m_next, n_next);
-#endif
+            ts_u32 next_range = 0, next_ws = kNoTail;
+            if (has_next) {
+                ts_u32 tile;
+                unit_of(u + tile_step, full_tiles, splits, num_k_blocks, tile, next_range, next_ws);
+                scales_of_tile(m_next, n_next, next_range & 0xffffu, next_range >> 16);
+            }
             // ---- epilogue from registers (alpha is already in the scales): bias, cast, swizzled staging, TMA
             // store.  The warp fills all its staging buffers, then one fence and one commit cover their stores.
+            if (un_ws != kNoTail) {
+                // ---- tail unit: the fp32 partial of this range of K blocks is added into the tile's workspace rows
+                // (32 columns per 128-byte staging row); bias and cast wait for the kernel that closes the tail.
+                constexpr ts_u32 kTailChunks = kWarpCols / 32;
+                static_assert(kTailChunks % kStoreBufs == 0, "the tail's chunks must fill whole rounds of staging buffers");
+                const int ws_row0 = (int)(un_ws + cta_rank * kBlockM + quarter * 32);
+#pragma unroll
+                for (ts_u32 g = 0; g < kTailChunks / kStoreBufs; ++g) {
+                    if (lane == 0) ts_bulk_wait_read<0>();
+                    __syncwarp();
+#pragma unroll
+                    for (ts_u32 b = 0; b < kStoreBufs; ++b) {
+                        const ts_u32 j = g * kStoreBufs + b;
+                        const ts_u32 row_addr = store_smem + b * kStoreBuf + lane * 128;
+#pragma unroll
+                        for (ts_u32 c = 0; c < 8; ++c)
+                            ts_st_shared_v4(row_addr + ((c << 4) ^ row_sw), __float_as_uint(acc[j * 32 + 4 * c]),
+                                            __float_as_uint(acc[j * 32 + 4 * c + 1]), __float_as_uint(acc[j * 32 + 4 * c + 2]),
+                                            __float_as_uint(acc[j * 32 + 4 * c + 3]));
+                    }
+                    ts_fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+#pragma unroll
+                        for (ts_u32 b = 0; b < kStoreBufs; ++b)
+                            ts_tma_reduce_add_2d(&tmap_ws, store_smem + b * kStoreBuf,
+                                                 (int)(half * kWarpCols + (g * kStoreBufs + b) * 32), ws_row0);
+                        ts_bulk_commit();
+                    }
+                }
+                m_blk = m_next; n_blk = n_next; un_range = next_range; un_ws = next_ws;
+                continue;
+            }
             const int row0 = (int)(m_blk * kTileM + cta_rank * kBlockM + quarter * 32);
 #pragma unroll
             for (ts_u32 g = 0; g < kWarpChunks / kStoreBufs; ++g) {
@@ -440,10 +515,7 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
                     ts_bulk_commit();
                 }
             }
-#if !TS_SCALES_EARLY
-            if (has_next) scales_of_tile(m_next, n_next);
-#endif
-            m_blk = m_next; n_blk = n_next;
+            m_blk = m_next; n_blk = n_next; un_range = next_range; un_ws = next_ws;
         }
         if (lane == 0) ts_bulk_wait_all();
         __syncwarp();
@@ -455,5 +527,43 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
     if (warp_id == 1) {
         ts_tc_fence_after();
         ts_tmem_dealloc<TS_CTA_GROUP>(tmem_base, kTmemCols);
+    }
+}
+
+// Closes the stream-K tail: C = cast(workspace + bias) for the tail tiles, and the workspace is cleared for the next
+// call.  Grid (tail tiles, 8): block (x, y) takes rows [32y * TS_CTA_GROUP / 2 ...) of tail tile x; 256 threads, four
+// columns per thread and step.
+#define TS_CAT2(a, b) a##b
+#define TS_CAT(a, b) TS_CAT2(a, b)
+extern "C" __global__ void __launch_bounds__(256)
+TS_CAT(TS_KERNEL_NAME, _tail)(float* __restrict__ ws, void* __restrict__ c_out, const ts_u16* __restrict__ bias,
+                              int M, int N, long long ldc, int group_m, int full_tiles)
+{
+    using namespace ts_fp8;
+    const ts_u32 num_m = ((ts_u32)M + kTileM - 1) / kTileM;
+    const ts_u32 num_n = ((ts_u32)N + kBlockN - 1) / kBlockN;
+    ts_u32 m_blk, n_blk;
+    ts_decode_tile((ts_u32)full_tiles + blockIdx.x, num_m, num_n, (ts_u32)group_m, m_blk, n_blk);
+    constexpr ts_u32 kVecPerRow = kBlockN / 4;
+    constexpr ts_u32 kRowsPerBlock = kTileM / 8;
+    float4* wt = reinterpret_cast<float4*>(ws + (size_t)blockIdx.x * kTileM * kBlockN);
+    for (ts_u32 i = threadIdx.x; i < kRowsPerBlock * kVecPerRow; i += blockDim.x) {
+        const ts_u32 r = blockIdx.y * kRowsPerBlock + i / kVecPerRow, cv = i % kVecPerRow;
+        const size_t wi = (size_t)r * kVecPerRow + cv;
+        float4 v = wt[wi];
+        wt[wi] = make_float4(0.f, 0.f, 0.f, 0.f);
+        const ts_u32 row = m_blk * kTileM + r, col = n_blk * kBlockN + 4 * cv;
+        if (row >= (ts_u32)M || col >= (ts_u32)N) continue;
+#if TS_HAS_BIAS
+        const uint2 bb = __ldg(reinterpret_cast<const uint2*>(bias + col));
+        v.x += ts_bf16_lo_to_f32(bb.x); v.y += ts_bf16_hi_to_f32(bb.x);
+        v.z += ts_bf16_lo_to_f32(bb.y); v.w += ts_bf16_hi_to_f32(bb.y);
+#endif
+#if TS_OUT_F32
+        *reinterpret_cast<float4*>(static_cast<float*>(c_out) + (size_t)row * ldc + col) = v;
+#else
+        *reinterpret_cast<uint2*>(static_cast<ts_u16*>(c_out) + (size_t)row * ldc + col) =
+            make_uint2(ts_pack_bf16x2(v.x, v.y), ts_pack_bf16x2(v.z, v.w));
+#endif
     }
 }

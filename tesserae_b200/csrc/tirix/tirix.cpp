@@ -88,10 +88,16 @@ Program lower(const KernelConfig& c, const tesserae_kernel_spec& ks) {
 
     // Parameters in launch order.
     p.params = {{"A_tmap", true}, {"B_tmap", true}, {c.scatter ? "C_tmaps" : "C_tmap", true}};
+    if (c.grouped) p.params = {{"problem_table", false}, {"total_tiles", false}};   // the maps and sizes live in the table
     if (c.scatter) { p.params.push_back({"rows_per_owner", false}); p.params.push_back({"m_rotate", false}); }
-    if (fp8blk) { p.params.push_back({"scale_a", false}); p.params.push_back({"scale_b", false}); }
+    if (fp8blk) { p.params.push_back({"WS_tmap", true}); p.params.push_back({"scale_a", false}); p.params.push_back({"scale_b", false}); }
     if (nvfp4) { p.params.push_back({"SFA_tmap", true}); p.params.push_back({"SFB_tmap", true}); }
-    for (const char* n : {"bias", "alpha", "M", "N", "K", "group_m", "status"}) p.params.push_back({n, false});
+    for (const char* n : {"bias", "alpha", "M", "N", "K", "group_m"}) p.params.push_back({n, false});
+    if (fp8blk) { p.params.push_back({"full_tiles", false}); p.params.push_back({"tail_splits", false}); }
+    p.params.push_back({"status", false});
+    // (a grouped kernel reads the three maps from the table row of the tile it is on; they are named here so that
+    // the operations below can refer to them)
+    if (c.grouped) p.params.push_back({"A_tmap", true}), p.params.push_back({"B_tmap", true}), p.params.push_back({"C_tmap", true});
 
     // Tensors: global operands, the shared-memory ring (depth, rows, bytes of K : row-major inside a stage, the
     // layout the reference states column-major, lib/tirix/desc_to_tirix.ml:66-85), tensor memory, output staging.
@@ -589,7 +595,7 @@ std::string print(const Program& p) {
     const tesserae_kernel_spec& k = p.origin;
     o << "origin arch=" << k.arch << " elem=" << k.elem << " tile=" << k.tile_m << "," << k.tile_n << "," << k.tile_k << " stages=" << k.stages
       << " cta_group=" << k.cta_group << " out_elem=" << k.out_elem << " has_bias=" << k.has_bias << " scale_mode=" << k.scale_mode
-      << " scatter=" << k.scatter << " tuning=" << (p.origin_tuning.empty() ? "-" : p.origin_tuning) << "\n";
+      << " scatter=" << k.scatter << " grouped=" << k.grouped << " tuning=" << (p.origin_tuning.empty() ? "-" : p.origin_tuning) << "\n";
     for (auto& q : p.params) o << "param " << q.name << " " << (q.is_tma ? "tma" : "ptr") << "\n";
     for (auto& t : p.tensors)
         o << "tensor " << t.name << " space=" << t.space << " elem=" << t.elem << " swizzle=" << t.swizzle_b << " shape=" << join(t.shape)
@@ -640,6 +646,7 @@ bool parse(const std::string& text, Program* out, std::string* err) {
             k.stages = atoi(kv(toks, "stages", "0").c_str()); k.cta_group = atoi(kv(toks, "cta_group", "0").c_str());
             k.out_elem = atoi(kv(toks, "out_elem", "0").c_str()); k.has_bias = atoi(kv(toks, "has_bias", "0").c_str());
             k.scale_mode = atoi(kv(toks, "scale_mode", "0").c_str()); k.scatter = atoi(kv(toks, "scatter", "0").c_str());
+            k.grouped = atoi(kv(toks, "grouped", "0").c_str());
             const std::string tun = kv(toks, "tuning", "-");
             p.origin_tuning = tun == "-" ? "" : tun;
             ++ps.at;

@@ -49,6 +49,17 @@ def test_emit_rejects_what_the_reference_rejects():
         api.backend_emit(api.KernelSpec(name="k", elem=api.F8E4M3, tile=(128, 256, 64), scale_mode=api.SCALE_FP8_BLOCK))
 
 
+def test_grouped_kernel_takes_a_problem_table():
+    plain = api.backend_emit(api.KernelSpec(name="k", tile=(128, 256, 64), cta_group=2, out_elem=api.BF16))
+    grouped = api.backend_emit(api.KernelSpec(name="k", tile=(128, 256, 64), cta_group=2, out_elem=api.BF16, grouped=1))
+    assert "#define TS_GROUPED 1" in grouped.includes and "TS_GROUPED" not in plain.includes
+    with pytest.raises(api.TesseraeError, match="grouped launches are for the unscaled kernels"):
+        api.backend_emit(api.KernelSpec(name="k", tile=(128, 256, 64), cta_group=2, scatter=1, grouped=1))
+    with pytest.raises(api.TesseraeError, match="grouped launches are for the unscaled kernels"):
+        api.backend_emit(api.KernelSpec(name="k", elem=api.F8E4M3, tile=(128, 256, 128), scale_mode=api.SCALE_FP8_BLOCK, grouped=1))
+    assert api.grouped_workspace_bytes(3) == 4 * 448 and api.grouped_workspace_bytes(0) == 0
+
+
 def test_operand_swizzle_follows_the_tile():
     """Swizzle.smem_selector (lib/core/swizzle.ml:46-56) decides the operand tiles' swizzle from tile.k; the
     emitted kernel is specialised on that B, it is not a constant of the backend."""

@@ -167,3 +167,76 @@ def test_host_buffer_entry_point_equals_device_call(torch_cuda, m, n, k):
     plan.run_scaled_host(qa, qb, c, sa, sb, None, 1.0, m, n, k)
     assert plan.status() == 0
     assert np.array_equal(c.float().numpy(), want)
+
+
+def tail_plan(cg, out_elem, bias, tuning):
+    key = ("tail", cg, out_elem, bias, tuning)
+    if key not in _plans:
+        _plans[key] = api.GemmPlan(api.KernelSpec(name=f"gemm_fp8blk_tail_cg{cg}_o{out_elem}_b{bias}_{len(tuning)}", elem=api.F8E4M3,
+                                                  tile=(128, 256, 128), cta_group=cg, out_elem=out_elem, has_bias=bias,
+                                                  scale_mode=api.SCALE_FP8_BLOCK, tuning=tuning))
+    return _plans[key]
+
+
+@pytest.mark.parametrize("cg,out_elem,bias,tuning,shape", [
+    (2, api.BF16, 0, "", (8192, 1792, 1024)),                # the default rule: three whole waves of CTA pairs plus two tiles
+    (2, api.BF16, 0, "TAIL_SPLITS=8", (512, 1024, 2048)),    # asked for: less than half a wave, every tile is split along K
+    (2, api.F32, 1, "TAIL_SPLITS=16", (1000, 1016, 1536)),   # ragged edges, bias, fp32 out
+    (1, api.BF16, 0, "TAIL_SPLITS=4", (512, 1024, 1024)),
+])
+def test_stream_k_tail(torch_cuda, cg, out_elem, bias, tuning, shape):
+    """The workspace entry point: tiles past the last whole wave are computed as K ranges added into the workspace.
+    Whole tiles are bit-equal to the plain entry point, tail tiles agree with the oracle, the workspace is left
+    clear, and a second call through the same workspace gives the same answer within rounding."""
+    torch = torch_cuda
+    m, n, k = shape
+    plan = tail_plan(cg, out_elem, bias, tuning)
+    nbytes = plan.tail_workspace_bytes(m, n, k)
+    assert nbytes > 0, "this shape is meant to have a tail on a B200"
+    p = O.make_fp8_problem(m, n, k, seed=900 + m % 7, with_bias=bool(bias))
+    ref = O.gemm_f32(p["a"], p["b"], 0.5, p["bias"])
+    plain = run_scaled(torch, plan, p, m, n, k, out_elem, alpha=0.5)
+    qa, qb = torch.from_numpy(p["qa"]).cuda(), torch.from_numpy(p["qb"]).cuda()
+    sa, sb = torch.from_numpy(p["sa"]).cuda(), torch.from_numpy(p["sb"]).cuda()
+    bias_d = torch.from_numpy(p["bias_bits"].view(np.int16)).view(torch.bfloat16).cuda() if bias else None
+    ws = torch.zeros(nbytes // 4, dtype=torch.float32, device="cuda")
+    tol = 1e-3 if out_elem == api.F32 else TOL_FP8
+    for _ in range(2):
+        c = torch.full((m, n), float("nan"), dtype=torch.bfloat16 if out_elem == api.BF16 else torch.float32, device="cuda")
+        plan.run_scaled_ws(qa, qb, c, sa, sb, ws, nbytes, bias_d, 0.5, m, n, k, stream=torch.cuda.current_stream().cuda_stream)
+        assert plan.status() == 0
+        got = c.float().cpu().numpy()
+        assert not np.isnan(got).any()
+        assert O.rel_error(got, ref)["max_rel"] <= tol
+        assert int(torch.count_nonzero(ws)) == 0, "the closing kernel leaves the workspace clear"
+        same = got == plain
+        # the entries that differ at all lie in the tail tiles and differ by rounding only
+        assert np.abs(got - plain).max() <= 2e-2 * max(1.0, float(np.abs(plain).max()))
+        tail_tiles = nbytes // (128 * cg * 256 * 4)
+        assert (~same).sum() <= tail_tiles * 128 * cg * 256
+
+
+def test_tail_workspace_rules(torch_cuda):
+    torch = torch_cuda
+    assert plan_for(2, 256).tail_workspace_bytes(8192, 9472, 4096) == 0     # 1184 tiles = 16 whole waves of 74 CTA pairs
+    assert plan_for(2, 256).tail_workspace_bytes(8192, 14336, 4096) == 0    # 16 tiles left over: more than one cluster in sixteen
+    assert plan_for(2, 256).tail_workspace_bytes(512, 1024, 2048) == 0      # less than a wave
+    assert plan_for(2, 256).tail_workspace_bytes(8192, 1792, 4096) == 2 * 256 * 256 * 4
+    plan = tail_plan(2, api.BF16, 0, "TAIL_SPLITS=8")
+    m, n, k = 512, 1024, 2048
+    need = plan.tail_workspace_bytes(m, n, k)
+    p = O.make_fp8_problem(m, n, k, seed=5)
+    qa, qb = torch.from_numpy(p["qa"]).cuda(), torch.from_numpy(p["qb"]).cuda()
+    sa, sb = torch.from_numpy(p["sa"]).cuda(), torch.from_numpy(p["sb"]).cuda()
+    c = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    ws = torch.zeros(need // 4, dtype=torch.float32, device="cuda")
+    with pytest.raises(api.TesseraeError, match="tail workspace too small"):
+        plan.run_scaled_ws(qa, qb, c, sa, sb, ws, need - 4, None, 1.0, m, n, k)
+    # a plan told never to split takes no workspace and runs whole tiles
+    whole = api.GemmPlan(api.KernelSpec(name="gemm_fp8blk_cg2_n256_notail", elem=api.F8E4M3, tile=(128, 256, 128), cta_group=2,
+                                        out_elem=api.BF16, scale_mode=api.SCALE_FP8_BLOCK, tuning="TAIL_SPLITS=1"))
+    assert whole.tail_workspace_bytes(m, n, k) == 0
+    whole.run_scaled_ws(qa, qb, c, sa, sb, None, 0, None, 1.0, m, n, k)
+    torch.cuda.synchronize()
+    assert whole.status() == 0
+    assert O.rel_error(c.float().cpu().numpy(), O.gemm_f32(p["a"], p["b"]))["max_rel"] <= TOL_FP8

@@ -212,3 +212,55 @@ def test_operand_swizzle_derived_from_tile_k(torch_cuda, cg, tile_k, swizzle_b):
         e = O.rel_error(got, O.gemm_f32(p["a"], p["b"]))
         assert e["max_rel"] <= TOL_F32_OUT, (cg, tile_k, m, n, k, e)
     plan.close()
+
+
+GROUPED_SHAPES = [(512, 512, 512), (200, 264, 72), (1, 8, 8), (129, 8, 520), (1000, 1016, 1032), (64, 4096, 128),
+                  (4096, 64, 128), (256, 256, 64)]
+
+
+def test_grouped_launch_equals_one_launch_per_problem(torch_cuda):
+    """One grouped launch over ragged problems: bit-equal to the ungrouped kernel run problem by problem (the
+    tile arithmetic is the same code), and within the bf16 tolerance of the oracle."""
+    torch = torch_cuda
+    spec = dict(elem=api.BF16, tile=(128, 256, 64), cta_group=2, out_elem=api.BF16, has_bias=1)
+    grouped = api.GemmPlan(api.KernelSpec(name="gemm_bf16_cg2_bf16_grouped", grouped=1, **spec))
+    single = plan_for(2, api.BF16, 1)
+    st = torch.cuda.current_stream().cuda_stream
+    keep, problems, refs, singles = [], [], [], []
+    for i, (m, n, k) in enumerate(GROUPED_SHAPES):
+        p = O.make_bf16_problem(m, n, k, seed=700 + i, with_bias=True)
+        a, b, bias = to_dev(torch, p["a_bits"]), to_dev(torch, p["b_bits"]), to_dev(torch, p["bias_bits"])
+        c = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+        c1 = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+        single.run(a, b, c1, bias, 0.75, m, n, k, stream=st)
+        keep.append((a, b, bias, c))
+        problems.append((a, b, c, bias, m, n, k))
+        refs.append(O.gemm_f32(p["a"], p["b"], 0.75, p["bias"]))
+        singles.append(c1)
+    nbytes = api.grouped_workspace_bytes(len(problems))
+    ws = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    for _ in range(2):                                   # the second call reuses the plan's pinned table
+        grouped.run_grouped(problems, ws, nbytes, alpha=0.75, stream=st)
+    torch.cuda.synchronize()
+    assert grouped.status() == 0 and single.status() == 0
+    for (m, n, k), (_, _, _, c), c1, ref in zip(GROUPED_SHAPES, keep, singles, refs):
+        assert torch.equal(c.view(torch.int16), c1.view(torch.int16)), (m, n, k)
+        assert O.rel_error(c.float().cpu().numpy(), ref)["max_rel"] <= TOL_BF16_OUT, (m, n, k)
+
+
+def test_grouped_argument_errors(torch_cuda):
+    torch = torch_cuda
+    grouped = api.GemmPlan(api.KernelSpec(name="gemm_bf16_cg2_bf16_grouped", elem=api.BF16, tile=(128, 256, 64), cta_group=2,
+                                          out_elem=api.BF16, has_bias=1, grouped=1))
+    a = torch.zeros(128, 64, dtype=torch.bfloat16, device="cuda")
+    c = torch.zeros(128, 128, dtype=torch.bfloat16, device="cuda")
+    bias = torch.zeros(128, dtype=torch.bfloat16, device="cuda")
+    ws = torch.empty(4096, dtype=torch.uint8, device="cuda")
+    with pytest.raises(api.TesseraeError, match="workspace too small"):
+        grouped.run_grouped([(a, a, c, bias, 128, 128, 64)], ws, 448)
+    with pytest.raises(api.TesseraeError, match="problem 1: .*bias"):
+        grouped.run_grouped([(a, a, c, bias, 128, 128, 64), (a, a, c, None, 128, 128, 64)], ws, 4096)
+    with pytest.raises(api.TesseraeError, match="use tesserae_gemm_run_grouped"):
+        grouped.run(a, a, c, bias, 1.0, 128, 128, 64)
+    with pytest.raises(api.TesseraeError, match="grouped = 1"):
+        plan_for(2, api.BF16, 1).run_grouped([(a, a, c, bias, 128, 128, 64)], ws, 4096)
