@@ -678,6 +678,8 @@ def main():
                     help="also measure fp8_block, nvfp4 and bf16_ksplit in the same process (default: all for the "
                          "headline workload, none otherwise)")
     ap.add_argument("--sustained-seconds", type=float, default=1.0)
+    ap.add_argument("--no-cublas-leg", action="store_true",
+                    help="skip the same-process cuBLAS comparison and the one-second sustained legs (short runs under a profiler)")
     ap.add_argument("--tuning", default="", help="tuning string of the main workload's kernel spec, e.g. GROUP_M=4 or TAIL_SPLITS=1")
     ap.add_argument("--ksplit-exchange", default="reduce", choices=["reduce", "fused", "nccl"],
                     help="K-split at 2+ GPUs: tiles added into the owner's buffer by the GEMM's own stores (reduce), stored "
@@ -717,7 +719,7 @@ def main():
         line["e2e"]["copy_probe"] = pcie_probe(wl, world, dev)
 
     # ---- the headline kernel against cuBLAS in the same process, both regimes, with the clock seen
-    if w["kind"] == "bf16" and w["m"] >= 4096:
+    if w["kind"] == "bf16" and w["m"] >= 4096 and not args.no_cublas_leg:
         flops_one = 2.0 * wl.m * wl.n * wl.k
         bt = wl.b.t()
         cub = lambda: torch.matmul(wl.a, bt)

@@ -429,15 +429,15 @@ int tesserae_gemm_run_scaled(tesserae_gemm_plan* plan, const void* a, const void
                              const tesserae_gemm_scales* scales, const void* bias,
                              float alpha, int64_t m, int64_t n, int64_t k, void* stream);
 /* ------------------------------------------------------------------ stream-K tail (FP8 block-scaled)
- * tesserae_gemm_run_scaled with a workspace: when the problem's tile count leaves a nearly empty last wave, the tiles
- * past the last whole wave are split into ranges of K blocks that all CTAs share; their fp32 partial sums are added
- * into the workspace and a closing kernel adds the bias, casts into C and clears the workspace again.  The role is the
- * one the reference reserves for a scheduler (lib/pipeline/cluster.mli:17-21); it has no counterpart there.
+ * tesserae_gemm_run_scaled with a workspace, for plans whose spec's tuning has TAIL_SPLITS=n (n >= 2; the kernel is
+ * then compiled with the unit logic below; opt-in, because on the shapes measured it wins nothing over running the
+ * left-over tiles as a last wave):
+ * when tiles are left over after the last whole wave and fill at most half the resident clusters, each of them is
+ * split into at most n ranges of K blocks that all CTAs share; the fp32 partial sums are added into the workspace and
+ * a closing kernel adds the bias, casts into C and clears the workspace again.  The role is the one the reference
+ * reserves for a scheduler (lib/pipeline/cluster.mli:17-21); it has no counterpart there.
  *   tesserae_gemm_tail_workspace_bytes: bytes the call below needs for this problem on this plan (0: no tail is used,
- *   the workspace may be NULL).  By default a tail is used only when the left-over tiles would occupy at most one
- *   cluster in sixteen after at least one whole wave (where it was measured to pay); tuning TAIL_SPLITS=n (n >= 2)
- *   asks for it whenever the left-over tiles fill at most half the clusters, with at most n ranges per tile;
- *   TAIL_SPLITS=1 never splits.
+ *   the workspace may be NULL; always 0 for plans without TAIL_SPLITS).
  *   The workspace must be 128-byte aligned and ZERO-FILLED before its first use; every call leaves it zero-filled.
  *   After a call whose tesserae_gemm_status is not 0, clear it again.
  * The additions into the workspace happen in no fixed order: the tail tiles' results can differ in the last bit from

@@ -266,6 +266,7 @@ BackendOutput emit(const KernelConfig& c) {
     o.includes = buf;
     if (c.scatter) o.includes += "#define TS_SCATTER " + std::to_string(c.scatter) + "\n";
     if (c.grouped) o.includes += "#define TS_GROUPED 1\n";
+    if (c.scale_mode == TESSERAE_SCALE_FP8_BLOCK && c.tail_splits >= 2) o.includes += "#define TS_FP8_TAIL 1\n";
     if (c.scale_mode == TESSERAE_SCALE_NONE) o.includes += "#define TS_STORE_BUFS " + std::to_string(c.store_bufs) + "\n";
     if (c.scale_mode == TESSERAE_SCALE_FP8_BLOCK) {
         o.includes += std::string("#define TS_FP8_SPLIT ") + (c.fp8_split ? "1\n" : "0\n");

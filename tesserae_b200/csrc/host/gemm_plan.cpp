@@ -388,13 +388,14 @@ static int pick_group_m(const KernelConfig& cfg, int64_t m, int64_t k) {
 }
 
 // Stream-K tail of the FP8 block-scaled kernel: which tiles are computed whole and into how many ranges of K blocks
-// each of the rest is split.  The tail pays a pass over its tiles (workspace adds, closing kernel) and the fixed cost
-// of a unit, and the few tiles of a nearly empty last wave already run faster than tiles of a full wave (they have
-// the memory system to themselves), so what it wins is small.  Measured on a B200 (8192 x N x 4096, 74 clusters):
-// 2 tiles left over: 2 % faster; 4: even; 8 and 16: 1-2 % slower; problems of less than a wave: 7-37 % slower.
-// By default it is therefore used only when at least one whole wave runs and the tiles left over would occupy at
-// most one cluster in sixteen.  TAIL_SPLITS=n (n >= 2) in the spec's tuning asks for it whenever tiles are left over
-// that fill at most half the clusters (with at most n ranges), which is what the tests use to reach every path.
+// each of the rest is split.  Only plans whose spec asks for it (TAIL_SPLITS=n, n >= 2, in the tuning string) carry
+// the unit logic in their kernel, because what it wins is small.  Measured on a B200, 8192 x 1792 x 4096 (74 clusters,
+// 2 tiles left over after 3 whole waves): 72.7 us per call with the tail against 72.5 us without; per kernel (profiler,
+// cold caches): 65.1 us + the closing kernel against 70.0 us.  The left-over wave of two tiles costs 11.5 us, not a
+// whole wave's 19 us (two tiles alone have the memory system to themselves), the tail's units cost 6.6 us (pipeline
+// fill, one pass through the staging buffers, the adds) and the second launch takes most of the rest.  The same
+// problem without left-over tiles runs 2 % slower through a kernel compiled with the unit logic.
+// With it, a tail is used whenever tiles are left over after the whole waves and fill at most half the clusters.
 struct TailPlan { int64_t full_tiles = 0, tail_tiles = 0; int splits = 1; size_t bytes = 0; };
 static TailPlan plan_tail(const tesserae_gemm_plan* p, int64_t m, int64_t n, int64_t k) {
     const KernelConfig& cfg = p->cfg;
@@ -402,16 +403,13 @@ static TailPlan plan_tail(const tesserae_gemm_plan* p, int64_t m, int64_t n, int
     const int64_t tile_m = 128 * cfg.cta_group;
     const int64_t tiles = ((m + tile_m - 1) / tile_m) * ((n + cfg.block_n - 1) / cfg.block_n);
     t.full_tiles = tiles;
-    if (cfg.scale_mode != TESSERAE_SCALE_FP8_BLOCK || cfg.tail_splits == 1) return t;
+    if (cfg.scale_mode != TESSERAE_SCALE_FP8_BLOCK || cfg.tail_splits < 2) return t;
     const int64_t clusters = p->max_clusters, nkb = k / 128;
     const int64_t rest = tiles % clusters;
-    if (rest == 0 || nkb < 4) return t;
-    const bool asked = cfg.tail_splits >= 2;
-    if (asked ? rest * 2 > clusters : (tiles < clusters || rest * 16 > clusters)) return t;
+    if (rest == 0 || nkb < 4 || rest * 2 > clusters) return t;
     int64_t splits = clusters / rest;
     if (splits > nkb / 2) splits = nkb / 2;              // at least two K blocks per unit
-    if (splits > 16) splits = 16;
-    if (asked && splits > cfg.tail_splits) splits = cfg.tail_splits;
+    if (splits > cfg.tail_splits) splits = cfg.tail_splits;
     if (splits < 2) return t;
     t.full_tiles = tiles - rest;
     t.tail_tiles = rest;
@@ -515,7 +513,7 @@ static int gemm_launch(tesserae_gemm_plan* p, const void* a, int64_t lda, const 
             {&gmi, sizeof(int)}, {&full_i, sizeof(int)}, {&splits_i, sizeof(int)}, {&p->d_status, sizeof(void*)}};
         rc = tesserae_launch_kernel_ex(p->function, ugrid, block, cluster, cfg.smem_bytes, stream, args, 15);
         if (rc != 0 || tp.tail_tiles == 0) return rc;
-        const int tgrid[3] = {int(tp.tail_tiles), 8, 1};
+        const int tgrid[3] = {int(tp.tail_tiles), 32, 1};
         const int tblock[3] = {256, 1, 1};
         const int one[3] = {1, 1, 1};
         const long long ldc_ll = ldc;

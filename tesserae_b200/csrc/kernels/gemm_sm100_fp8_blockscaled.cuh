@@ -34,9 +34,11 @@
 //    clears the workspace.  With a tile count a little over a whole number of waves this replaces a last wave
 //    of a few tiles, one whole K loop long, by a wave of K-range units a fraction as long.  The order of the
 //    additions into the workspace is not fixed, so tail tiles are not bit-reproducible from run to run.
+//    Compiled in only with TS_FP8_TAIL (the host's notes give the measurements: it breaks even at best).
 //
 // Compile-time configuration (macros): TS_KERNEL_NAME, TS_CTA_GROUP (1|2), TS_BLOCK_N (128|256),
-// TS_STAGES, TS_PROMO_WARPS (8|16), TS_OUT_F32, TS_HAS_BIAS, TS_FP8_SPLIT.
+// TS_STAGES, TS_PROMO_WARPS (8|16), TS_OUT_F32, TS_HAS_BIAS, TS_FP8_SPLIT, TS_FP8_TAIL (0|1: without it the unit logic
+// of the stream-K tail folds away at compile time and every unit is a whole tile).
 #pragma once
 
 #ifndef TS_PROMO_WARPS
@@ -91,9 +93,13 @@ static_assert(kSmemTotal + 1024 <= 232448, "shared memory over the 227 KB limit"
 
 // One unit of work: a tile and a range of its K blocks.  `range` packs first block | blocks << 16 (K < 2^23);
 // `ws_row` is the unit's first workspace row, or kNoTail for a whole tile.
+#ifndef TS_FP8_TAIL
+#define TS_FP8_TAIL 0
+#endif
+constexpr bool kTail = TS_FP8_TAIL != 0;
 constexpr ts_u32 kNoTail = 0xffffffffu;
 TS_DEV void unit_of(ts_u32 u, ts_u32 full_tiles, ts_u32 splits, ts_u32 num_k_blocks, ts_u32& tile, ts_u32& range, ts_u32& ws_row) {
-    if (u < full_tiles) { tile = u; range = num_k_blocks << 16; ws_row = kNoTail; return; }
+    if (!kTail || u < full_tiles) { tile = u; range = num_k_blocks << 16; ws_row = kNoTail; return; }
     const ts_u32 v = u - full_tiles, ti = v / splits, part = v - ti * splits;
     const ts_u32 kb0 = part * num_k_blocks / splits;
     tile = full_tiles + ti;
@@ -102,13 +108,43 @@ TS_DEV void unit_of(ts_u32 u, ts_u32 full_tiles, ts_u32 splits, ts_u32 num_k_blo
 }
 // The same for a role that only needs the unit's number of K blocks.
 TS_DEV ts_u32 unit_blocks_of(ts_u32 u, ts_u32 full_tiles, ts_u32 splits, ts_u32 num_k_blocks) {
-    if (u < full_tiles) return num_k_blocks;
+    if (!kTail || u < full_tiles) return num_k_blocks;
     const ts_u32 part = (u - full_tiles) % splits;
     return (part + 1) * num_k_blocks / splits - part * num_k_blocks / splits;
 }
 
 TS_DEV void ts_tmem_ld(ts_u32 taddr, ts_u32 (&r)[16]) { ts_tmem_ld_32x32b_x16(taddr, r); }
 TS_DEV void ts_tmem_ld(ts_u32 taddr, ts_u32 (&r)[32]) { ts_tmem_ld_32x32b_x32(taddr, r); }
+
+// A tail unit's epilogue: this warp's 32 rows x kWarpCols fp32 partial sums (one row per lane, handed over in local
+// memory) go through the warp's staging buffers, 32 columns per 128-byte row, and are added into the workspace by TMA.
+__device__ __noinline__ void tail_add(const float* part, ts_u32 store_smem, ts_u32 row_sw, ts_u32 lane,
+                                      const TsTensorMap* tmap_ws, int col0, int ws_row0) {
+    constexpr ts_u32 kTailChunks = kWarpCols / 32;
+    static_assert(kTailChunks % kStoreBufs == 0, "the tail's chunks must fill whole rounds of staging buffers");
+#pragma unroll 1
+    for (ts_u32 g = 0; g < kTailChunks / kStoreBufs; ++g) {
+        if (lane == 0) ts_bulk_wait_read<0>();       // the stores that last read the staging buffers
+        __syncwarp();
+#pragma unroll 1
+        for (ts_u32 b = 0; b < kStoreBufs; ++b) {
+            const float* src = part + (g * kStoreBufs + b) * 32;
+            const ts_u32 row_addr = store_smem + b * kStoreBuf + lane * 128;
+#pragma unroll
+            for (ts_u32 c = 0; c < 8; ++c)
+                ts_st_shared_v4(row_addr + ((c << 4) ^ row_sw), __float_as_uint(src[4 * c]), __float_as_uint(src[4 * c + 1]),
+                                __float_as_uint(src[4 * c + 2]), __float_as_uint(src[4 * c + 3]));
+        }
+        ts_fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+            for (ts_u32 b = 0; b < kStoreBufs; ++b)
+                ts_tma_reduce_add_2d(tmap_ws, store_smem + b * kStoreBuf, col0 + (int)((g * kStoreBufs + b) * 32), ws_row0);
+            ts_bulk_commit();
+        }
+        __syncwarp();
+    }
+}
 
 }  // namespace ts_fp8
 
@@ -148,9 +184,9 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
     const ts_u32 num_k_blocks = ((ts_u32)K + kBlockK - 1) / kBlockK;
     // (the host passes full_tiles <= tiles and 1 <= tail_splits <= K blocks; used as they come, so that they can be
     // re-read from the parameter bank instead of being held in registers across the promotion loop)
-    const ts_u32 full_tiles = (ts_u32)full_tiles_arg;
-    const ts_u32 splits = (ts_u32)tail_splits_arg;
-    const ts_u32 num_units = full_tiles + (num_tiles - full_tiles) * splits;
+    const ts_u32 full_tiles = kTail ? (ts_u32)full_tiles_arg : num_tiles;
+    const ts_u32 splits = kTail ? (ts_u32)tail_splits_arg : 1u;
+    const ts_u32 num_units = kTail ? full_tiles + (num_tiles - full_tiles) * splits : num_tiles;
     const ts_u32 first_tile = (TS_CTA_GROUP == 2) ? ts_cluster_id_x() : blockIdx.x;
     const ts_u32 tile_step  = (TS_CTA_GROUP == 2) ? ts_nclusters_x() : gridDim.x;
 
@@ -158,7 +194,7 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
         ts_prefetch_tmap(&tmap_a);
         ts_prefetch_tmap(&tmap_b);
         ts_prefetch_tmap(&tmap_c);
-        if (full_tiles < num_tiles) ts_prefetch_tmap(&tmap_ws);
+        if (kTail && full_tiles < num_tiles) ts_prefetch_tmap(&tmap_ws);
         for (ts_u32 s = 0; s < kStages; ++s) {
             ts_mbar_init(full_bar + 8 * s, 1);
             ts_mbar_init(empty_bar + 8 * s, kHalves);          // one commit per issuing warp
@@ -192,7 +228,7 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
             bool ok = true;
             for (ts_u32 u = first_tile; u < num_units && ok; u += tile_step) {
                 ts_u32 tile = u, kb_begin = 0, kb_end = num_k_blocks;
-                if (u >= full_tiles) {
+                if (kTail && u >= full_tiles) {
                     const ts_u32 v = u - full_tiles, ti = v / splits, part = v - ti * splits;
                     tile = full_tiles + ti;
                     kb_begin = part * num_k_blocks / splits;
@@ -318,10 +354,10 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
         ts_u32 m_blk = 0, n_blk = 0;
         const bool fast_decode = num_tiles < (1u << 22);
         const float inv_group = 1.0f / (float)((ts_u32)group_m * num_n), inv_gm = 1.0f / (float)group_m;
-        ts_u32 un_range = 0, un_ws = kNoTail;
+        ts_u32 un_range = 0;
         if (first_tile < num_units) {
-            ts_u32 tile;
-            unit_of(first_tile, full_tiles, splits, num_k_blocks, tile, un_range, un_ws);
+            ts_u32 tile, ws_unused;
+            unit_of(first_tile, full_tiles, splits, num_k_blocks, tile, un_range, ws_unused);
             ts_decode_tile(tile, num_m, num_n, (ts_u32)group_m, m_blk, n_blk);
             scales_of_tile(m_blk, n_blk, un_range & 0xffffu, un_range >> 16);
         }
@@ -332,11 +368,11 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
                 // (the tile index of the next unit is one compare for a whole tile and a division for a tail unit; its
                 // range of K blocks is worked out after this unit's K loop, so that nothing more stays live across it)
                 const ts_u32 un = u + tile_step;
-                const ts_u32 tile = un < full_tiles ? un : full_tiles + (un - full_tiles) / splits;
+                const ts_u32 tile = (!kTail || un < full_tiles) ? un : full_tiles + (un - full_tiles) / splits;
                 if (fast_decode) ts_decode_tile_fast(tile, num_m, num_n, (ts_u32)group_m, inv_group, inv_gm, m_next, n_next);
                 else             ts_decode_tile(tile, num_m, num_n, (ts_u32)group_m, m_next, n_next);
             }
-            const ts_u32 nkb = un_range >> 16;
+            const ts_u32 nkb = kTail ? un_range >> 16 : nkb_all;
             const ts_u32 col_base = n_blk * kBlockN + half * kWarpCols;
             // 128 x BLOCK_N fp32 accumulators of the tile, one row per lane, held as packed pairs: the multiply-adds
             // are issued two at a time (fma.rn.f32x2: the same two roundings as two scalar fmas, half the issue slots).
@@ -427,37 +463,19 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
             }
             // ---- epilogue from registers (alpha is already in the scales): bias, cast, swizzled staging, TMA
             // store.  The warp fills all its staging buffers, then one fence and one commit cover their stores.
-            if (un_ws != kNoTail) {
-                // ---- tail unit: the fp32 partial of this range of K blocks is added into the tile's workspace rows
-                // (32 columns per 128-byte staging row); bias and cast wait for the kernel that closes the tail.
-                constexpr ts_u32 kTailChunks = kWarpCols / 32;
-                static_assert(kTailChunks % kStoreBufs == 0, "the tail's chunks must fill whole rounds of staging buffers");
-                const int ws_row0 = (int)(un_ws + cta_rank * kBlockM + quarter * 32);
+            // (a tail unit's workspace row is worked out here, from the unit index, rather than carried across the K loop)
+            const ts_u32 un_ws = (kTail && u >= full_tiles) ? ((u - full_tiles) / splits) * kTileM : kNoTail;
+            if (kTail && un_ws != kNoTail) {
+                // ---- tail unit: the fp32 partial of this range of K blocks is added into the tile's workspace rows;
+                // bias and cast wait for the kernel that closes the tail.  The accumulators are handed over through
+                // local memory to a function that is not inlined: with this second epilogue inline the compiler
+                // allocates the promotion loop's registers differently and every tile is a tenth slower (measured).
+                float part[kWarpCols];
 #pragma unroll
-                for (ts_u32 g = 0; g < kTailChunks / kStoreBufs; ++g) {
-                    if (lane == 0) ts_bulk_wait_read<0>();
-                    __syncwarp();
-#pragma unroll
-                    for (ts_u32 b = 0; b < kStoreBufs; ++b) {
-                        const ts_u32 j = g * kStoreBufs + b;
-                        const ts_u32 row_addr = store_smem + b * kStoreBuf + lane * 128;
-#pragma unroll
-                        for (ts_u32 c = 0; c < 8; ++c)
-                            ts_st_shared_v4(row_addr + ((c << 4) ^ row_sw), __float_as_uint(acc[j * 32 + 4 * c]),
-                                            __float_as_uint(acc[j * 32 + 4 * c + 1]), __float_as_uint(acc[j * 32 + 4 * c + 2]),
-                                            __float_as_uint(acc[j * 32 + 4 * c + 3]));
-                    }
-                    ts_fence_proxy_async_smem();
-                    __syncwarp();
-                    if (lane == 0) {
-#pragma unroll
-                        for (ts_u32 b = 0; b < kStoreBufs; ++b)
-                            ts_tma_reduce_add_2d(&tmap_ws, store_smem + b * kStoreBuf,
-                                                 (int)(half * kWarpCols + (g * kStoreBufs + b) * 32), ws_row0);
-                        ts_bulk_commit();
-                    }
-                }
-                m_blk = m_next; n_blk = n_next; un_range = next_range; un_ws = next_ws;
+                for (ts_u32 i = 0; i < kWarpCols; ++i) part[i] = acc[i];
+                tail_add(part, store_smem, row_sw, lane, &tmap_ws, (int)(half * kWarpCols),
+                         (int)(un_ws + cta_rank * kBlockM + quarter * 32));
+                m_blk = m_next; n_blk = n_next; un_range = next_range;
                 continue;
             }
             const int row0 = (int)(m_blk * kTileM + cta_rank * kBlockM + quarter * 32);
@@ -515,7 +533,7 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
                     ts_bulk_commit();
                 }
             }
-            m_blk = m_next; n_blk = n_next; un_range = next_range; un_ws = next_ws;
+            m_blk = m_next; n_blk = n_next; un_range = next_range;
         }
         if (lane == 0) ts_bulk_wait_all();
         __syncwarp();
@@ -531,8 +549,9 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
 }
 
 // Closes the stream-K tail: C = cast(workspace + bias) for the tail tiles, and the workspace is cleared for the next
-// call.  Grid (tail tiles, 8): block (x, y) takes rows [32y * TS_CTA_GROUP / 2 ...) of tail tile x; 256 threads, four
-// columns per thread and step.
+// call.  Grid (tail tiles, kTailBlocksY): a block takes tile rows / kTailBlocksY rows of one tail tile, 256 threads,
+// four columns per thread and step -- one or two steps per thread, so that the pass is a single round trip to L2
+// and not a chain of them.
 #define TS_CAT2(a, b) a##b
 #define TS_CAT(a, b) TS_CAT2(a, b)
 extern "C" __global__ void __launch_bounds__(256)
@@ -545,10 +564,10 @@ TS_CAT(TS_KERNEL_NAME, _tail)(float* __restrict__ ws, void* __restrict__ c_out, 
     ts_u32 m_blk, n_blk;
     ts_decode_tile((ts_u32)full_tiles + blockIdx.x, num_m, num_n, (ts_u32)group_m, m_blk, n_blk);
     constexpr ts_u32 kVecPerRow = kBlockN / 4;
-    constexpr ts_u32 kRowsPerBlock = kTileM / 8;
+    const ts_u32 rows_per_block = kTileM / gridDim.y;
     float4* wt = reinterpret_cast<float4*>(ws + (size_t)blockIdx.x * kTileM * kBlockN);
-    for (ts_u32 i = threadIdx.x; i < kRowsPerBlock * kVecPerRow; i += blockDim.x) {
-        const ts_u32 r = blockIdx.y * kRowsPerBlock + i / kVecPerRow, cv = i % kVecPerRow;
+    for (ts_u32 i = threadIdx.x; i < rows_per_block * kVecPerRow; i += blockDim.x) {
+        const ts_u32 r = blockIdx.y * rows_per_block + i / kVecPerRow, cv = i % kVecPerRow;
         const size_t wi = (size_t)r * kVecPerRow + cv;
         float4 v = wt[wi];
         wt[wi] = make_float4(0.f, 0.f, 0.f, 0.f);

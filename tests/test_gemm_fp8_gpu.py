@@ -179,7 +179,7 @@ def tail_plan(cg, out_elem, bias, tuning):
 
 
 @pytest.mark.parametrize("cg,out_elem,bias,tuning,shape", [
-    (2, api.BF16, 0, "", (8192, 1792, 1024)),                # the default rule: three whole waves of CTA pairs plus two tiles
+    (2, api.BF16, 0, "TAIL_SPLITS=16", (8192, 1792, 1024)),  # three whole waves of CTA pairs plus two tiles (one GPU's share of config 3 on 8)
     (2, api.BF16, 0, "TAIL_SPLITS=8", (512, 1024, 2048)),    # asked for: less than half a wave, every tile is split along K
     (2, api.F32, 1, "TAIL_SPLITS=16", (1000, 1016, 1536)),   # ragged edges, bias, fp32 out
     (1, api.BF16, 0, "TAIL_SPLITS=4", (512, 1024, 1024)),
@@ -218,11 +218,11 @@ def test_stream_k_tail(torch_cuda, cg, out_elem, bias, tuning, shape):
 
 def test_tail_workspace_rules(torch_cuda):
     torch = torch_cuda
-    assert plan_for(2, 256).tail_workspace_bytes(8192, 9472, 4096) == 0     # 1184 tiles = 16 whole waves of 74 CTA pairs
-    assert plan_for(2, 256).tail_workspace_bytes(8192, 14336, 4096) == 0    # 16 tiles left over: more than one cluster in sixteen
-    assert plan_for(2, 256).tail_workspace_bytes(512, 1024, 2048) == 0      # less than a wave
-    assert plan_for(2, 256).tail_workspace_bytes(8192, 1792, 4096) == 2 * 256 * 256 * 4
+    assert plan_for(2, 256).tail_workspace_bytes(8192, 1792, 4096) == 0     # a plan that did not ask for it never splits
     plan = tail_plan(2, api.BF16, 0, "TAIL_SPLITS=8")
+    assert plan.tail_workspace_bytes(8192, 9472, 4096) == 0                 # 1184 tiles = 16 whole waves of 74 CTA pairs
+    assert plan.tail_workspace_bytes(8192, 3328, 4096) == 0                 # 416 tiles: the 46 left over fill more than half the clusters
+    assert plan.tail_workspace_bytes(8192, 1792, 4096) == 2 * 256 * 256 * 4
     m, n, k = 512, 1024, 2048
     need = plan.tail_workspace_bytes(m, n, k)
     p = O.make_fp8_problem(m, n, k, seed=5)
