@@ -57,7 +57,7 @@ WORKLOADS = {
 SUB_CONFIGS = ["fp8_block", "nvfp4", "bf16_ksplit"]
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel, from the ncu
 # captures summarised under profiles/; None where no capture exists.
-TRAFFIC_BYTES = {"bf16_8192_bias": 1.2437e9, "fp8_block": 4.737e8, "nvfp4": 2.2376e9}
+TRAFFIC_BYTES = {"bf16_8192_bias": 1.2138e9, "fp8_block": 3.291e8, "nvfp4": 1.5667e9}
 
 
 def measured_peaks():
