@@ -66,6 +66,9 @@ enum {
 
 /* Swizzle.apply (lib/core/swizzle.ml:15-17): x ^ ((x & (((1<<b)-1) << (m+s))) >> s) */
 int64_t tesserae_swizzle_apply(int b, int m, int s, int64_t offset);
+/* Swizzle.apply_to_layout (lib/core/swizzle.ml:36-43): the swizzle applied to every stride leaf (flattened, n leaves);
+ * shapes are unchanged.  Returns 0, or -1 on a negative parameter. */
+int tesserae_swizzle_apply_to_strides(int b, int m, int s, const int64_t* stride, int n, int64_t* out_stride);
 /* Swizzle.smem_selector (lib/core/swizzle.ml:46-56); writes b,m,s */
 int tesserae_swizzle_smem_selector(int elem, int tile_m, int tile_k, int* b, int* m, int* s);
 /* Elemtype.byte_width / bits / vec_width (lib/core/elemtype.ml:24-57); -1 for a bad code.

@@ -191,6 +191,13 @@ def swizzle_apply(sw, offset: int) -> int:
     return offset ^ ((offset & mask) >> s)
 
 
+def swizzle_apply_to_layout(sw, layout):
+    """lib/core/swizzle.ml:36-43: every stride leaf goes through the swizzle; the shape is kept."""
+    def walk(m):
+        return swizzle_apply(sw, m) if isinstance(m, int) else tuple(walk(x) for x in m)
+    return Layout(layout.shape, walk(layout.stride))
+
+
 def swizzle_compose(a, b):
     if a[1] != b[1] or a[2] != b[2]:
         raise ValueError("incompatible swizzle shifts for composition")

@@ -99,6 +99,7 @@ SIGNATURES = {
     "tesserae_elem_bits": (C.c_int, [C.c_int]),
     "tesserae_elem_vec_width": (C.c_int, [C.c_int]),
     "tesserae_layout_size": (C.c_int64, [_I64P, C.c_int]),
+    "tesserae_swizzle_apply_to_strides": (C.c_int, [C.c_int, C.c_int, C.c_int, _I64P, C.c_int, _I64P]),
     "tesserae_layout_cosize": (C.c_int64, [_I64P, _I64P, C.c_int]),
     "tesserae_layout_idx": (C.c_int64, [_I64P, _I64P, C.c_int]),
     "tesserae_layout_compose": (C.c_int, [_I64P, _I64P, C.c_int, _I64P, _I64P, C.c_int, _I64P]),

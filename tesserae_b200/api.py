@@ -415,6 +415,14 @@ def swizzle_smem_selector(elem: int, tile_m: int, tile_k: int):
     return b.value, m.value, s.value
 
 
+def swizzle_apply_to_strides(b: int, m: int, s: int, stride):
+    """Swizzle.apply_to_layout on the flattened strides of a layout (its shape does not change)."""
+    d, n = _arr(stride)
+    out = (C.c_int64 * max(n, 1))()
+    check(N.lib().tesserae_swizzle_apply_to_strides(b, m, s, d, n, out), "swizzle_apply_to_strides")
+    return [out[i] for i in range(n)]
+
+
 def layout_cosize(shape, stride) -> int:
     s, n = _arr(shape)
     d, _ = _arr(stride)

@@ -28,6 +28,14 @@ extern "C" {
 int64_t tesserae_swizzle_apply(int b, int m, int s, int64_t offset) {
     TS_GUARD(return sp::swizzle_apply(sp::swizzle_make(b, m, s), offset));
 }
+int tesserae_swizzle_apply_to_strides(int b, int m, int s, const int64_t* stride, int n, int64_t* out_stride) {
+    if (!stride || !out_stride || n < 0) return fail("swizzle_apply_to_strides: null argument");
+    try {
+        const sp::Swizzle sw = sp::swizzle_make(b, m, s);
+        for (int i = 0; i < n; ++i) out_stride[i] = sp::swizzle_apply(sw, stride[i]);
+        return 0;
+    } catch (const std::exception& e) { return fail(e.what()); }
+}
 int tesserae_swizzle_smem_selector(int elem, int tile_m, int tile_k, int* b, int* m, int* s) {
     TS_GUARD({
         sp::Swizzle sw = sp::swizzle_smem_selector(elem, tile_m, tile_k);

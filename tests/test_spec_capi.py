@@ -214,6 +214,22 @@ def test_random_swizzle_matches_oracle():
         assert api.swizzle_apply(b, m, s, x) == L.swizzle_apply((b, m, s), x)
 
 
+def test_swizzle_apply_to_layout_matches_oracle():
+    """Swizzle.apply_to_layout: leaf-wise on the strides, nested in the oracle, flattened in the product."""
+    rng = random.Random(11)
+    lay = L.Layout((2, (3, 4)), (1, (2, 6)))
+    assert L.flatten(L.swizzle_apply_to_layout((0, 4, 3), lay).stride) == [1, 2, 6]          # Swizzle<0,...> is the identity
+    assert api.swizzle_apply_to_strides(3, 4, 3, [1023, 128, 1]) == [911, 144, 1]               # 1023 -> 911 (test_swizzle.ml:43-46)
+    for _ in range(300):
+        b, m, s = rng.randint(0, 4), rng.randint(0, 6), rng.randint(0, 4)
+        strides = (rng.randrange(1 << 14), (rng.randrange(1 << 14), rng.randrange(1 << 14)))
+        want = L.swizzle_apply_to_layout((b, m, s), L.Layout((2, (2, 2)), strides))
+        assert want.shape == (2, (2, 2))
+        assert api.swizzle_apply_to_strides(b, m, s, L.flatten(strides)) == L.flatten(want.stride)
+    with pytest.raises(api.TesseraeError, match="non-negative"):
+        api.swizzle_apply_to_strides(-1, 4, 3, [1])
+
+
 def test_hardware_descriptors():
     """The descriptors the kernels build on the device, restated on the host: field positions
     of the sm_100 shared-memory matrix descriptor and instruction descriptor."""
