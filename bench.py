@@ -346,6 +346,8 @@ class Workload:
                 if ev:
                     ev[1].record()
                 hdl.barrier(channel=0)
+                if ev:
+                    ev[3].record()
                 api.reduce_cast_bf16(stag[buf], self.world, rows * self.n, self.c, rows * self.n, stream=self.stream)
                 if ev:
                     ev[2].record()
@@ -378,6 +380,8 @@ class Workload:
                 if ev:
                     ev[1].record()
                 hdl.barrier(channel=0)
+                if ev:
+                    ev[3].record()
                 api.cast_clear_bf16(acc[buf], self.c, rows * self.n, stream=self.stream)
                 if ev:
                     ev[2].record()
@@ -403,6 +407,8 @@ class Workload:
                 ev[1].record()
             if self.world > 1:
                 dist.reduce_scatter_tensor(self.mine, self.partial, op=dist.ReduceOp.SUM)
+            if ev:
+                ev[3].record()
             api.reduce_cast_bf16(self.mine, slices, self.m * self.n if slices > 1 else 0, self.c, self.c.numel(),
                                  stream=self.stream)
             if ev:
@@ -528,7 +534,7 @@ def measure(name, w, rank, local_rank, world, dev, args, exchange="fused", extra
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     # K-split: every timed step also records (start, GEMM done, exchange + cast done), so that the compute and the
     # exchange shares come from the same steps, under the same clocks, as the step time itself
-    marks = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)] if w["kind"] == "ksplit" else None
+    marks = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)] if w["kind"] == "ksplit" else None
     e0.record()
     for i in range(args.steps):
         if marks:
@@ -556,7 +562,8 @@ def measure(name, w, rank, local_rank, world, dev, args, exchange="fused", extra
     # ---- K-split: compute and communication separately, means over the timed steps
     split = None
     if marks:
-        split = [sum(m[0].elapsed_time(m[1]) for m in marks) / len(marks), sum(m[1].elapsed_time(m[2]) for m in marks) / len(marks)]
+        split = [sum(m[0].elapsed_time(m[1]) for m in marks) / len(marks), sum(m[1].elapsed_time(m[2]) for m in marks) / len(marks),
+                 sum(m[1].elapsed_time(m[3]) for m in marks) / len(marks), sum(m[3].elapsed_time(m[2]) for m in marks) / len(marks)]
 
     # ---- end to end from pinned host buffers
     wl.e2e_step()
@@ -570,11 +577,12 @@ def measure(name, w, rank, local_rank, world, dev, args, exchange="fused", extra
     torch.cuda.synchronize()
     max_rel = wl.check()
 
-    vals = [elapsed_ms, e2e_ms, float(status), max_rel, min(burst_ms)] + (split or [0.0, 0.0])
+    sp = split or [0.0, 0.0, 0.0, 0.0]
+    vals = [elapsed_ms, e2e_ms, float(status), max_rel, min(burst_ms)] + sp + [-sp[0], -sp[2]]
     tt = torch.tensor(vals, dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-    elapsed_ms, e2e_ms, status, max_rel, burst, gemm_ms, comm_ms = tt.tolist()
+    elapsed_ms, e2e_ms, status, max_rel, burst, gemm_ms, comm_ms, wait_ms, cast_ms, neg_gemm_min, neg_wait_min = tt.tolist()
 
     flops_step = wl.flops_total()
     ms_per_step = elapsed_ms / args.steps
@@ -606,7 +614,11 @@ def measure(name, w, rank, local_rank, world, dev, args, exchange="fused", extra
     if split:
         rec["ksplit"] = {"exchange": exchange if world > 1 else "none", "gemm_ms": gemm_ms,
                          "reduce_scatter_plus_cast_ms": comm_ms,
-                         "exposed_after_gemm_ms": ms_per_step - gemm_ms}
+                         "exposed_after_gemm_ms": ms_per_step - gemm_ms,
+                         # the part after the GEMM, split at the end of the barrier / collective; max and min over the
+                         # ranks: a rank whose GEMM ends early spends the difference waiting in the barrier
+                         "gemm_ms_min_rank": -neg_gemm_min, "barrier_or_collective_ms": wait_ms,
+                         "barrier_or_collective_ms_min_rank": -neg_wait_min, "sum_cast_ms": cast_ms}
     return rec, wl, sync_all
 
 
@@ -681,7 +693,7 @@ def main():
     ap.add_argument("--no-cublas-leg", action="store_true",
                     help="skip the same-process cuBLAS comparison and the one-second sustained legs (short runs under a profiler)")
     ap.add_argument("--tuning", default="", help="tuning string of the main workload's kernel spec, e.g. GROUP_M=4 or TAIL_SPLITS=1")
-    ap.add_argument("--ksplit-exchange", default="reduce", choices=["reduce", "fused", "nccl"],
+    ap.add_argument("--ksplit-exchange", default="fused", choices=["reduce", "fused", "nccl"],
                     help="K-split at 2+ GPUs: tiles added into the owner's buffer by the GEMM's own stores (reduce), stored "
                          "to per-source slots and summed by the owner (fused), or NCCL reduce-scatter of plain partials")
     args = ap.parse_args()
@@ -755,25 +767,30 @@ def main():
                 continue
             sw = WORKLOADS[name]
             try:
-                srec, swl, _ = measure(name, sw, rank, local_rank, world, dev, args, exchange="reduce")
+                srec, swl, _ = measure(name, sw, rank, local_rank, world, dev, args, exchange="fused")
                 if sw["kind"] == "ksplit" and world > 1:
                     keep = ("value", "ms_per_step", "ksplit", "max_rel_err_vs_oracle_sample", "kernel_status",
                             "pct_of_nominal_dense_peak")
-                    outs = {"reduce": swl.c.clone()}
-                    for other in ("fused", "nccl"):
+                    outs = {"fused": swl.c.clone()}
+                    for other in ("reduce", "nccl"):
                         swl.close(); del swl
                         torch.cuda.empty_cache()
                         orec, swl, _ = measure(name, sw, rank, local_rank, world, dev, args, exchange=other)
                         outs[other] = swl.c.clone()
                         srec[other] = {k: orec[k] for k in keep}
                     flags = []
+                    ref = outs["nccl"].float()
+                    ulp = torch.exp2(torch.floor(torch.log2(ref.abs().clamp_min(2.0 ** -100))) - 7)   # one bf16 step at each value
                     for x in ("reduce", "fused"):
                         same = torch.equal(outs[x].view(torch.int16), outs["nccl"].view(torch.int16))
-                        flags += [0.0 if same else 1.0, float((outs[x].float() - outs["nccl"].float()).abs().max())]
+                        d = (outs[x].float() - ref).abs()
+                        flags += [0.0 if same else 1.0, float(d.max()), float((d / ulp).max())]
                     flags = torch.tensor(flags, dtype=torch.float64, device=dev)
                     dist.all_reduce(flags, op=dist.ReduceOp.MAX)
-                    srec["reduce_equals_nccl"], srec["reduce_vs_nccl_max_abs_diff"] = flags[0].item() == 0.0, flags[1].item()
-                    srec["fused_equals_nccl"], srec["fused_vs_nccl_max_abs_diff"] = flags[2].item() == 0.0, flags[3].item()
+                    for j, x in enumerate(("reduce", "fused")):
+                        srec[f"{x}_equals_nccl"] = flags[3 * j].item() == 0.0
+                        srec[f"{x}_vs_nccl_max_abs_diff"] = flags[3 * j + 1].item()
+                        srec[f"{x}_vs_nccl_max_bf16_ulps"] = flags[3 * j + 2].item()
                     srec["exchange_note"] = ("all three exchanges sum the same fp32 partials: `reduce` in the order the tiles "
                                              "arrive at the owner, `fused` in rank order, NCCL in its ring order; with 2 ranks "
                                              "the sums are equal to the bit, beyond that the bf16 results may differ in the "

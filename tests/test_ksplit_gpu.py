@@ -199,7 +199,7 @@ def test_cast_clear(torch_cuda):
     """tesserae_cast_clear_bf16: the cast of the adding epilogue's buffer, which leaves the buffer zeroed; same
     rounding as tesserae_reduce_cast_bf16 of one partial, ragged length included."""
     t = torch_cuda
-    for n in (8 * 1024 + 5, 3, 1 << 20):
+    for n in (8 * 1024 + 5, 3, 1 << 20, (1 << 24) + 7):        # the last one takes several passes of the whole grid
         acc = t.randn(n + 3, device="cuda")[:n].contiguous() if n % 4 else t.randn(n, device="cuda")
         want = t.empty(n, dtype=t.bfloat16, device="cuda")
         api.reduce_cast_bf16(acc, 1, 0, want, n, alpha=0.5, stream=t.cuda.current_stream().cuda_stream)
