@@ -780,17 +780,18 @@ def main():
                         srec[other] = {k: orec[k] for k in keep}
                     flags = []
                     ref = outs["nccl"].float()
-                    ulp = torch.exp2(torch.floor(torch.log2(ref.abs().clamp_min(2.0 ** -100))) - 7)   # one bf16 step at each value
+                    # one bf16 step at the largest output magnitude: a difference of that size is one rounding apart
+                    step = float(torch.exp2(torch.floor(torch.log2(ref.abs().max().clamp_min(2.0 ** -100))) - 7))
                     for x in ("reduce", "fused"):
                         same = torch.equal(outs[x].view(torch.int16), outs["nccl"].view(torch.int16))
                         d = (outs[x].float() - ref).abs()
-                        flags += [0.0 if same else 1.0, float(d.max()), float((d / ulp).max())]
+                        flags += [0.0 if same else 1.0, float(d.max()), float(d.max()) / step]
                     flags = torch.tensor(flags, dtype=torch.float64, device=dev)
                     dist.all_reduce(flags, op=dist.ReduceOp.MAX)
                     for j, x in enumerate(("reduce", "fused")):
                         srec[f"{x}_equals_nccl"] = flags[3 * j].item() == 0.0
                         srec[f"{x}_vs_nccl_max_abs_diff"] = flags[3 * j + 1].item()
-                        srec[f"{x}_vs_nccl_max_bf16_ulps"] = flags[3 * j + 2].item()
+                        srec[f"{x}_vs_nccl_max_diff_in_bf16_steps_of_max_abs"] = flags[3 * j + 2].item()
                     srec["exchange_note"] = ("all three exchanges sum the same fp32 partials: `reduce` in the order the tiles "
                                              "arrive at the owner, `fused` in rank order, NCCL in its ring order; with 2 ranks "
                                              "the sums are equal to the bit, beyond that the bf16 results may differ in the "

@@ -246,6 +246,12 @@ typedef struct tesserae_kernel_spec {
      *   STORE_BUFS=2..4        dense kernel: staging buffers per epilogue warp
      *   FP8_PROMO_WARPS=8|16   block-scaled FP8: promotion warps
      *   FP8_SPLIT=0|1          block-scaled FP8: one MMA chain per tile width / per 128 columns
+     *   TAIL_SPLITS=0..64      block-scaled FP8: stream-K tail (tesserae_gemm_run_scaled_ws); 0 or 1 = none
+     *   CLC=0|1                unscaled kernels without scatter: tile order by cluster launch control.  The grid has
+     *                          one cluster per tile; a seventh warp (the Scheduler role of lib/pipeline/cluster.mli:17-21)
+     *                          cancels clusters that have not started and feeds their tiles to the running ones, so
+     *                          tiles of unequal length are balanced dynamically.  Results are bit-identical to the
+     *                          static order's.
      * An unknown name or a value out of range fails with IncompatibleTile. */
     const char* tuning;
     int grouped;     /* 1: the kernel walks a list of problems (tesserae_gemm_run_grouped); unscaled kernels, no scatter */

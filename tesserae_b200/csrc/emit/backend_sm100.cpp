@@ -20,9 +20,10 @@ constexpr int kSmemLimit = 232448;   // 227 KB of dynamic shared memory per CTA 
 
 // Dynamic shared memory of each kernel family; mirrors kSmemTotal in the .cuh plus the
 // 1024-byte alignment slack.
-int dense_smem_bytes(int cta_group, int block_n, int stages, int store_bufs, int row_bytes) {
+int dense_smem_bytes(int cta_group, int block_n, int stages, int store_bufs, int row_bytes, int clc) {
     const int stage = (128 + block_n / cta_group) * row_bytes;
-    return stages * stage + 4 * store_bufs * 4096 + (2 * stages + 4) * 8 + 16 + 1024;
+    const int sched = clc ? (2 * 4 + 1) * 8 + 48 : 0;     // the scheduler's ring: barriers, answer, tile ids
+    return stages * stage + 4 * store_bufs * 4096 + (2 * stages + 4) * 8 + 16 + sched + 1024;
 }
 int fp8_smem_bytes(int cta_group, int block_n, int stages, int promo_warps, int out_bytes) {
     const int stage = 128 * 128 + (block_n / cta_group) * 128;
@@ -44,7 +45,7 @@ int smem_bytes_for(const KernelConfig& c, int stages) {
     const int ob = c.out_elem == TESSERAE_F32 ? 4 : 2;
     if (c.scale_mode == TESSERAE_SCALE_FP8_BLOCK) return fp8_smem_bytes(c.cta_group, c.block_n, stages, c.promo_warps, ob);
     if (c.scale_mode == TESSERAE_SCALE_NVFP4) return nvfp4_smem_bytes(c.cta_group, c.block_n, stages);
-    return dense_smem_bytes(c.cta_group, c.block_n, stages, c.store_bufs, 16 << c.desc.swizzle.b);
+    return dense_smem_bytes(c.cta_group, c.block_n, stages, c.store_bufs, 16 << c.desc.swizzle.b, c.clc);
 }
 
 std::string sanitize(const char* name) {
@@ -151,6 +152,7 @@ int derive_config(const tesserae_kernel_spec& ks, KernelConfig* cfg, std::string
             else if (key == "FP8_PROMO_WARPS") { ok = v == 8 || v == 16; want_promo_warps = v; }
             else if (key == "FP8_SPLIT") { ok = v == 0 || v == 1; c.fp8_split = v; }
             else if (key == "TAIL_SPLITS") { ok = v >= 0 && v <= 64; c.tail_splits = v; }
+            else if (key == "CLC") { ok = v == 0 || v == 1; c.clc = v; }
             else { if (msg) *msg = "IncompatibleTile: unknown tuning name '" + key + "'"; return spec::IncompatibleTile; }
             if (!ok) {
                 if (msg) *msg = "IncompatibleTile: tuning value out of range: " + key + "=" + std::to_string(v);
@@ -162,6 +164,11 @@ int derive_config(const tesserae_kernel_spec& ks, KernelConfig* cfg, std::string
     c.block_n = ks.tile_n;
     c.block_k = ks.tile_k;
     c.threads = spec::thread_count(desc.cluster);
+    if (c.clc && (ks.scale_mode != TESSERAE_SCALE_NONE || c.scatter)) {
+        if (msg) *msg = "IncompatibleTile: the cluster-launch-control scheduler is for the unscaled kernels without scattered output";
+        return spec::IncompatibleTile;
+    }
+    if (c.clc) c.threads += 32;        // the scheduler warp (Cluster's Scheduler role, lib/pipeline/cluster.mli:17-21)
 
     // What the hand-written mainloops cover: 128 rows per CTA, one swizzle row of K per stage, N a multiple
     // of the store chunk and of 16 per CTA.  The swizzle is the one Swizzle.smem_selector derives from the tile
@@ -266,6 +273,7 @@ BackendOutput emit(const KernelConfig& c) {
     o.includes = buf;
     if (c.scatter) o.includes += "#define TS_SCATTER " + std::to_string(c.scatter) + "\n";
     if (c.grouped) o.includes += "#define TS_GROUPED 1\n";
+    if (c.clc) o.includes += "#define TS_CLC 1\n";
     if (c.scale_mode == TESSERAE_SCALE_FP8_BLOCK && c.tail_splits >= 2) o.includes += "#define TS_FP8_TAIL 1\n";
     if (c.scale_mode == TESSERAE_SCALE_NONE) o.includes += "#define TS_STORE_BUFS " + std::to_string(c.store_bufs) + "\n";
     if (c.scale_mode == TESSERAE_SCALE_FP8_BLOCK) {

@@ -22,6 +22,7 @@ struct KernelConfig {
     int scale_mode = TESSERAE_SCALE_NONE;
     int scatter = 0;         // row-scattered output (dense kernel only): 1 stored to per-source slots, 2 added into the owner's buffer
     int tail_splits = 0;     // FP8 block-scaled, stream-K tail: 0 = the host chooses per launch, 1 = never, n = at most n K ranges per tail tile
+    int clc = 0;             // dense kernels: tile order by cluster launch control (scheduler warp) instead of the static walk
     int grouped = 0;         // the kernel walks a table of problems instead of one problem's tiles (dense kernel only)
     int promo_warps = 0;     // promotion warps of the FP8 block-scaled kernel (0 elsewhere)
     int store_bufs = 2;      // dense kernel: staging buffers per epilogue warp (4 when the stores cross NVLink)

@@ -468,7 +468,10 @@ static int gemm_launch(tesserae_gemm_plan* p, const void* a, int64_t lda, const 
 
     const int64_t tile_m = 128 * cfg.cta_group;
     const int64_t tiles = ((m + tile_m - 1) / tile_m) * ((n + cfg.block_n - 1) / cfg.block_n);
-    const int clusters = int(tiles < p->max_clusters ? tiles : p->max_clusters);
+    // Static order: one cluster per SM (pair), each walks every n-th tile.  Launch control: one cluster per tile; those
+    // that get to run take over the tiles of those that have not started yet.
+    if (cfg.clc && tiles * cfg.cta_group > INT32_MAX) return fail("gemm_run: too many tiles for a launch-control grid");
+    const int clusters = cfg.clc ? int(tiles) : int(tiles < p->max_clusters ? tiles : p->max_clusters);
     const int grid[3] = {clusters * cfg.cta_group, 1, 1};
     const int block[3] = {cfg.threads, 1, 1};
     const int cluster[3] = {cfg.cta_group, 1, 1};
@@ -628,7 +631,10 @@ int tesserae_gemm_run_grouped(tesserae_gemm_plan* p, const tesserae_gemm_problem
     e = cudaMemcpyAsync(workspace, rows, need, cudaMemcpyHostToDevice, st);
     if (e == cudaSuccess) e = cudaEventRecord(p->ev_table, st);
     if (e != cudaSuccess) return fail(std::string("gemm_run_grouped: ") + cudaGetErrorString(e));
-    const int clusters = int(tiles < p->max_clusters ? tiles : p->max_clusters);
+    // Static order: one cluster per SM (pair), each walks every n-th tile.  Launch control: one cluster per tile; those
+    // that get to run take over the tiles of those that have not started yet.
+    if (cfg.clc && tiles * cfg.cta_group > INT32_MAX) return fail("gemm_run_grouped: too many tiles for a launch-control grid");
+    const int clusters = cfg.clc ? int(tiles) : int(tiles < p->max_clusters ? tiles : p->max_clusters);
     const int grid[3] = {clusters * cfg.cta_group, 1, 1};
     const int block[3] = {cfg.threads, 1, 1};
     const int cluster[3] = {cfg.cta_group, 1, 1};

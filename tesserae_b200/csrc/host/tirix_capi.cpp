@@ -69,13 +69,8 @@ int tesserae_tirix_verify(const tesserae_tirix* t, char** errors) {
 
 int tesserae_tirix_count_ops(const tesserae_tirix* t, const char* op_name) {
     if (!t || !op_name) return -1;
-    static const char* const names[] = {
-        "Copy", "Mma", "CtaSync", "WarpSync", "MemFence", "MbarInit", "MbarArriveExpect", "MbarWaitParity", "MbarArrive",
-        "ClusterArrive", "ClusterWait", "CpAsyncWaitAll", "CpAsyncCommitGroup", "BulkCommit", "BulkWaitRead",
-        "Tcgen05WaitLd", "Tcgen05WaitSt", "Tcgen05FenceBefore", "Tcgen05FenceAfter", "TmemAlloc", "TmemDealloc", "TmemLoad",
-        "TmemStore", "TmemCommit", "SmemDescInit", "ScaleFma", "StoreShared"};
-    for (size_t i = 0; i < sizeof names / sizeof names[0]; ++i)
-        if (strcmp(names[i], op_name) == 0) return tx::count_ops(t->program, tx::OpKind(int(i)));
+    const int kind = tx::op_kind_from_name(op_name);
+    if (kind >= 0) return tx::count_ops(t->program, tx::OpKind(kind));
     fail(std::string("tirix_count_ops: unknown operation '") + op_name + "'");
     return -1;
 }

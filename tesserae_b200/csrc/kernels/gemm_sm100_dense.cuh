@@ -51,8 +51,20 @@
 //                    problem whose [tile_start, next tile_start) holds it, and every role looks its problem up as
 //                    it moves from tile to tile.  Tiles of different problems fill one wave together, so a list of
 //                    small problems is not quantised problem by problem.
+//   TS_CLC           0/1: dynamic tile order by cluster launch control -- the role the reference reserves a warp for
+//                    (lib/pipeline/cluster.mli:17-21: "Scheduler: issues CLC try_cancel, feeds tile ids").  The grid
+//                    has one cluster per tile instead of one per SM (pair).  Every cluster that runs computes its own
+//                    tile and then, through its scheduler warp (warp 6 of the leader CTA), asks the hardware to
+//                    cancel a cluster that has not started yet and takes that cluster's tile, until no cluster is
+//                    left to cancel.  A cluster that finishes a short tile early takes the next tile at once, so
+//                    tiles of unequal length (a grouped launch of problems with different K) do not wait for a
+//                    fixed round-robin turn.  Tile ids go to the roles of both CTAs through a ring of kSchedRing
+//                    entries in shared memory with a full and an empty barrier per entry.
 #pragma once
 
+#ifndef TS_CLC
+#define TS_CLC 0
+#endif
 #ifndef TS_GROUPED
 #define TS_GROUPED 0
 #endif
@@ -106,9 +118,13 @@ constexpr ts_u32 kNumEpiWarps = 4;
 #endif
 constexpr ts_u32 kStoreBufs   = TS_STORE_BUFS;                // staging buffers per epilogue warp (stores in flight + 1)
 constexpr ts_u32 kSmemC       = kNumEpiWarps * kStoreBufs * kStoreBuf;
-constexpr ts_u32 kNumBars     = 2 * kStages + 2 * kNumAcc;
-constexpr ts_u32 kSmemTotal   = kStages * kStageBytes + kSmemC + kNumBars * 8 + 16;
-constexpr ts_u32 kThreads     = 192;
+constexpr ts_u32 kSchedRing   = 4;                            // tile ids in flight between the scheduler warp and the roles
+constexpr ts_u32 kNumBars     = 2 * kStages + 2 * kNumAcc + (TS_CLC ? 2 * kSchedRing + 1 : 0);
+constexpr ts_u32 kSmemTotal   = kStages * kStageBytes + kSmemC + kNumBars * 8 + 16 + (TS_CLC ? 48 : 0);
+constexpr ts_u32 kThreads     = 192 + (TS_CLC ? 32 : 0);      // producer, MMA issuer, four epilogue warps (+ scheduler)
+constexpr ts_u32 kNoTile      = 0xffffffffu;
+// Arrivals that hand a ring entry back: the producer lane of each CTA, the MMA warp (leader only), the epilogue warps.
+constexpr ts_u32 kSchedReaders = TS_CTA_GROUP + 1 + kNumEpiWarps * TS_CTA_GROUP;
 
 static_assert(kBlockN % (16 * TS_CTA_GROUP) == 0 && kBlockN >= 16 * TS_CTA_GROUP && kBlockN <= 256, "bad TS_BLOCK_N");
 static_assert(kBlockN % kChunkCols == 0, "TS_BLOCK_N must be a multiple of the store chunk");
@@ -123,8 +139,10 @@ struct TileInfo {
     const ts_u16* bias;
 };
 #if TS_GROUPED
-// `cursor` is the problem the previous tile of this role belonged to; tiles only move forward.
+// `cursor` is the problem the previous tile of this role belonged to: with the static order tiles only move forward;
+// a dynamic order may hand out an earlier tile, and the search starts over.
 TS_DEV TileInfo tile_info(const TsGroupedProblem* probs, ts_u32 t, ts_u32& cursor) {
+    if (TS_CLC && t < (ts_u32)__ldg(&probs[cursor].tile_start)) cursor = 0;
     while (t >= (ts_u32)__ldg(&probs[cursor + 1].tile_start)) ++cursor;
     const TsGroupedProblem* pr = probs + cursor;
     TileInfo ti;
@@ -140,7 +158,7 @@ TS_DEV TileInfo tile_info(const TsGroupedProblem* probs, ts_u32 t, ts_u32& curso
 
 }  // namespace ts_dense
 
-extern "C" __global__ void __launch_bounds__(192, 1)
+extern "C" __global__ void __launch_bounds__(192 + (TS_CLC ? 32 : 0), 1)
 #if TS_GROUPED
 TS_KERNEL_NAME(const TsGroupedProblem* __restrict__ probs, int total_tiles, float alpha, ts_u32* __restrict__ status)
 #else
@@ -168,7 +186,16 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
     const ts_u32 empty_bar      = full_bar + 8 * kStages;         // [kStages]
     const ts_u32 tmem_full_bar  = empty_bar + 8 * kStages;        // [kNumAcc]
     const ts_u32 tmem_empty_bar = tmem_full_bar + 8 * kNumAcc;    // [kNumAcc]
+#if TS_CLC
+    const ts_u32 sched_full     = tmem_empty_bar + 8 * kNumAcc;   // [kSchedRing] entry j holds a tile id
+    const ts_u32 sched_empty    = sched_full + 8 * kSchedRing;    // [kSchedRing] every role of the pair has read it (leader CTA's)
+    const ts_u32 clc_bar        = sched_empty + 8 * kSchedRing;   // the launch control's answer has landed
+    const ts_u32 tmem_ptr_smem  = clc_bar + 8;                    // u32
+    const ts_u32 clc_response   = (tmem_ptr_smem + 4 + 15u) & ~15u;   // 16 bytes
+    const ts_u32 sched_ring     = clc_response + 16;              // [kSchedRing] u32
+#else
     const ts_u32 tmem_ptr_smem  = tmem_empty_bar + 8 * kNumAcc;   // u32
+#endif
 
     const ts_u32 warp_id  = threadIdx.x >> 5;
     const ts_u32 lane     = threadIdx.x & 31u;
@@ -213,6 +240,13 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
             ts_mbar_init(tmem_full_bar + 8 * b, 1);                               // one tcgen05.commit
             ts_mbar_init(tmem_empty_bar + 8 * b, kNumEpiWarps * TS_CTA_GROUP);    // one arrive per epilogue warp
         }
+#if TS_CLC
+        for (ts_u32 j = 0; j < kSchedRing; ++j) {
+            ts_mbar_init(sched_full + 8 * j, 1);                 // the scheduler's arrive (one per CTA, on that CTA's barrier)
+            ts_mbar_init(sched_empty + 8 * j, kSchedReaders);    // every reader of the pair, on the leader's barrier
+        }
+        ts_mbar_init(clc_bar, 1);
+#endif
         ts_fence_mbar_init();
     }
     if (TS_CTA_GROUP == 2) ts_cluster_sync();   // both CTAs of the pair are running before TMEM is split
@@ -226,6 +260,26 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
     ts_u32 tmem_base;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_ptr_smem) : "memory");
 
+#if TS_CLC
+    // The next tile of this cluster for a role that has walked `taken` tiles (its own first tile, then ring entries
+    // 0, 1, ...).  Every calling lane reads the entry; `releaser` (one lane per role instance) hands it back once the
+    // lanes that called together have read it (`warp_wide`: the whole warp calls).
+    const ts_u32 leader_sched_empty = ts_mapa(sched_empty, 0);
+    auto clc_next = [&](ts_u32& taken, bool& ok, bool releaser, bool warp_wide) -> ts_u32 {
+        const ts_u32 j = taken++, slot = j % kSchedRing;
+        if (!ts_mbar_wait_cluster(sched_full + 8 * slot, (j / kSchedRing) & 1u)) {
+            if (releaser) atomicOr(status, TS_ERR_TIMEOUT_SCHED);
+            ok = false;
+            return kNoTile;
+        }
+        ts_u32 t;
+        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(t) : "r"(sched_ring + 4 * slot) : "memory");
+        if (warp_wide) __syncwarp();
+        if (releaser) ts_mbar_arrive_release_cluster(leader_sched_empty + 8 * slot);
+        return t;
+    };
+#endif
+
     if (warp_id == 0) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
@@ -235,7 +289,12 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
 #if TS_GROUPED
             ts_u32 cursor = 0;
 #endif
+#if TS_CLC
+            ts_u32 taken = 0;
+            for (ts_u32 t = first_tile; t < num_tiles && ok; t = clc_next(taken, ok, true, false)) {
+#else
             for (ts_u32 t = first_tile; t < num_tiles && ok; t += tile_step) {
+#endif
 #if TS_GROUPED
                 const TileInfo ti = tile_info(probs, t, cursor);
                 const ts_u32 lt = ti.local_tile;
@@ -281,7 +340,12 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
 #if TS_GROUPED
             ts_u32 cursor = 0;
 #endif
+#if TS_CLC
+            ts_u32 taken = 0;
+            for (ts_u32 t = first_tile; t < num_tiles && ok; t = clc_next(taken, ok, elected, true), ++tile_iter) {
+#else
             for (ts_u32 t = first_tile; t < num_tiles && ok; t += tile_step, ++tile_iter) {
+#endif
 #if TS_GROUPED
                 const TileInfo ti = tile_info(probs, t, cursor);
 #endif
@@ -325,7 +389,7 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
             }
         }
         __syncwarp();
-    } else {
+    } else if (warp_id < 2 + kNumEpiWarps) {
         // ------------------------------------------------------------ epilogue (warps 2..5)
         const ts_u32 quarter = warp_id & 3u;             // TMEM lanes this warp may read
         const ts_u32 store_smem = smem_c + (warp_id - 2) * kStoreBufs * kStoreBuf;
@@ -336,7 +400,12 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
 #if TS_GROUPED
         ts_u32 cursor = 0;
 #endif
+#if TS_CLC
+        ts_u32 taken = 0;
+        for (ts_u32 t = first_tile; t < num_tiles && ok; t = clc_next(taken, ok, lane == 0, true), ++tile_iter) {
+#else
         for (ts_u32 t = first_tile; t < num_tiles && ok; t += tile_step, ++tile_iter) {
+#endif
 #if TS_GROUPED
             const TileInfo ti = tile_info(probs, t, cursor);
             const ts_u32 lt = ti.local_tile;
@@ -440,6 +509,35 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
         if (lane == 0) ts_bulk_wait_all();
         __syncwarp();
     }
+#if TS_CLC
+    else {
+        // ------------------------------------------------------------ scheduler (warp 6, leader CTA, one lane)
+        // Entry j of the ring: wait until every role of the pair has read what the entry held kSchedRing tiles ago,
+        // ask the launch control for one more cluster's tile, and publish the answer (a tile id, or kNoTile once
+        // nothing is left to cancel) to both CTAs: the id with a store to the CTA's shared memory, then an arrive
+        // with release at cluster scope on that CTA's full barrier.
+        if (is_leader && lane == 0) {
+            for (ts_u32 j = 0;; ++j) {
+                const ts_u32 slot = j % kSchedRing;
+                if (!ts_mbar_wait_cluster(sched_empty + 8 * slot, ((j / kSchedRing) & 1u) ^ 1u)) {
+                    atomicOr(status, TS_ERR_TIMEOUT_SCHED); break;
+                }
+                ts_mbar_arrive_expect_tx(clc_bar, 16);
+                ts_clc_try_cancel(clc_response, clc_bar);
+                if (!ts_mbar_wait(clc_bar, j & 1u)) { atomicOr(status, TS_ERR_TIMEOUT_SCHED); break; }
+                ts_u32 first_cta_x;
+                const bool got = ts_clc_query(clc_response, first_cta_x);
+                const ts_u32 t = got ? first_cta_x / TS_CTA_GROUP : kNoTile;
+                for (ts_u32 r = 0; r < TS_CTA_GROUP; ++r) {
+                    ts_st_shared_cluster_u32(ts_mapa(sched_ring + 4 * slot, r), t);
+                    ts_mbar_arrive_release_cluster(ts_mapa(sched_full + 8 * slot, r));
+                }
+                if (!got) break;       // (after a refusal no further request may be made)
+            }
+        }
+        __syncwarp();
+    }
+#endif
 
     // ---------------------------------------------------------------- teardown
     ts_tc_fence_before();

@@ -32,6 +32,7 @@ struct __align__(64) TsTensorMap { ts_u64 opaque[16]; };
 #define TS_ERR_TIMEOUT_SCALE      0x10u  // scale-factor pipeline ran out
 #define TS_ERR_BAD_TMEM_BASE      0x20u  // the two CTAs of a pair got different TMEM bases
 #define TS_ERR_TIMEOUT_TEST       0x40u  // the deliberately unsignalled barrier of the wait self-test
+#define TS_ERR_TIMEOUT_SCHED      0x80u  // the tile scheduler's ring (cluster launch control) ran out
 
 // tcgen05.mma kinds of the dense kernels.
 #define TS_KIND_F16     0
@@ -81,6 +82,23 @@ TS_DEV void ts_mbar_arrive(ts_u32 bar) {
 TS_DEV void ts_mbar_arrive_cluster(ts_u32 cluster_bar) {
     asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" :: "r"(cluster_bar) : "memory");
 }
+// The same with release semantics at cluster scope: what was written to the other CTA's shared memory before it
+// (st.shared::cluster) is visible to a thread there that waits with ts_mbar_wait_cluster.
+TS_DEV void ts_mbar_arrive_release_cluster(ts_u32 cluster_bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" :: "r"(cluster_bar) : "memory");
+}
+TS_DEV void ts_st_shared_cluster_u32(ts_u32 cluster_addr, ts_u32 v) {
+    asm volatile("st.shared::cluster.u32 [%0], %1;" :: "r"(cluster_addr), "r"(v) : "memory");
+}
+TS_DEV bool ts_mbar_try_wait_cluster(ts_u32 bar, ts_u32 parity) {
+    ts_u32 ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
 TS_DEV bool ts_mbar_try_wait(ts_u32 bar, ts_u32 parity) {
     ts_u32 ok;
     asm volatile(
@@ -105,6 +123,43 @@ TS_DEV bool ts_mbar_wait(ts_u32 bar, ts_u32 parity, ts_i64 budget = TS_WAIT_TIME
     }
     __syncwarp(peers);
     return __all_sync(peers, ok) != 0;
+}
+
+// Bounded wait with acquire at cluster scope (the barrier is signalled from another CTA of the cluster and guards
+// data that CTA wrote here).
+TS_DEV bool ts_mbar_wait_cluster(ts_u32 bar, ts_u32 parity, ts_i64 budget = TS_WAIT_TIMEOUT_CYCLES) {
+    if (ts_mbar_try_wait_cluster(bar, parity)) return true;
+    const ts_u32 peers = __activemask();
+    const ts_i64 t0 = clock64();
+    bool ok = true;
+    while (!ts_mbar_try_wait_cluster(bar, parity)) {
+        if (clock64() - t0 > budget) { ok = false; break; }
+    }
+    __syncwarp(peers);
+    return __all_sync(peers, ok) != 0;
+}
+
+// ---------------------------------------------------------------- cluster launch control
+// Asks the hardware to cancel the launch of one cluster of this grid that has not started yet.  The 16-byte answer
+// lands in this CTA's shared memory at `response` and completes 16 bytes on `bar`.  After an answer that says
+// "nothing was cancelled" no further request may be made by this cluster.
+TS_DEV void ts_clc_try_cancel(ts_u32 response, ts_u32 bar) {
+    asm volatile("clusterlaunchcontrol.try_cancel.async.shared::cta.mbarrier::complete_tx::bytes.b128 [%0], [%1];"
+                 :: "r"(response), "r"(bar) : "memory");
+}
+// Reads an answer: true and the x index of the cancelled cluster's first CTA, or false.
+TS_DEV bool ts_clc_query(ts_u32 response, ts_u32& first_cta_x) {
+    ts_u32 got, x;
+    asm volatile(
+        "{\n\t.reg .b128 r;\n\t.reg .pred p;\n\t"
+        "ld.shared.b128 r, [%2];\n\t"
+        "clusterlaunchcontrol.query_cancel.is_canceled.pred.b128 p, r;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "mov.u32 %1, 0;\n\t"
+        "@p clusterlaunchcontrol.query_cancel.get_first_ctaid::x.b32.b128 %1, r;\n\t}"
+        : "=r"(got), "=r"(x) : "r"(response) : "memory");
+    first_cta_x = x;
+    return got != 0;
 }
 
 // ---------------------------------------------------------------- TMA

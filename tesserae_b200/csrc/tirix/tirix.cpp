@@ -17,7 +17,7 @@ const char* const kOpNames[] = {
     "Copy", "Mma", "CtaSync", "WarpSync", "MemFence", "MbarInit", "MbarArriveExpect", "MbarWaitParity", "MbarArrive",
     "ClusterArrive", "ClusterWait", "CpAsyncWaitAll", "CpAsyncCommitGroup", "BulkCommit", "BulkWaitRead",
     "Tcgen05WaitLd", "Tcgen05WaitSt", "Tcgen05FenceBefore", "Tcgen05FenceAfter", "TmemAlloc", "TmemDealloc", "TmemLoad",
-    "TmemStore", "TmemCommit", "SmemDescInit", "ScaleFma", "StoreShared"};
+    "TmemStore", "TmemCommit", "SmemDescInit", "ScaleFma", "StoreShared", "ClcTryCancel", "ClcQuery", "StoreCluster"};
 constexpr int kNumOps = int(sizeof kOpNames / sizeof kOpNames[0]);
 const char* const kRoleNames[] = {"Producer", "Consumer", "Epilogue", "Scheduler"};
 
@@ -61,6 +61,8 @@ Stmt wait(const std::string& mbar, const std::string& phase, const std::string& 
 
 }  // namespace
 
+int op_kind_from_name(const std::string& name) { return op_from_name(name); }
+
 // ---------------------------------------------------------------- lowering
 Program lower(const KernelConfig& c, const tesserae_kernel_spec& ks) {
     Program p;
@@ -82,7 +84,8 @@ Program lower(const KernelConfig& c, const tesserae_kernel_spec& ks) {
     for (int w = 2; w < warps; ++w) {
         const bool second_issuer = fp8blk && c.fp8_split && c.block_n == 256 && w == 2;
         const bool idle = fp8blk && (w == 3 || (w == 2 && !second_issuer));
-        roles.push_back({w, second_issuer ? spec::Consumer : idle ? spec::Scheduler : spec::Epilogue});
+        const bool clc_sched = c.clc && w == warps - 1;
+        roles.push_back({w, second_issuer ? spec::Consumer : (idle || clc_sched) ? spec::Scheduler : spec::Epilogue});
     }
     p.cluster = spec::cluster_make(c.cta_group, 1, 1, warps, roles);
 
@@ -135,10 +138,16 @@ Program lower(const KernelConfig& c, const tesserae_kernel_spec& ks) {
     b.push_back(let("num_tiles", "num_m * num_n"));
     b.push_back(let("num_k_blocks", "(K + " + kblock + " - 1) / " + kblock));
     b.push_back(let("first_tile", pair ? "clusterid.x" : "blockIdx.x"));
-    b.push_back(let("tile_step", pair ? "nclusterid.x" : "gridDim.x"));
+    b.push_back(let("tile_step", c.clc ? "0" : pair ? "nclusterid.x" : "gridDim.x"));   // (launch control: the ring gives the next tile)
     for (const char* bar : {"full_bar", "empty_bar", "tmem_full_bar", "tmem_empty_bar"}) b.push_back(let(bar, "smem_barriers"));
     if (nvfp4) { b.push_back(let("sf_full_bar", "smem_barriers")); b.push_back(let("sf_ready_bar", "smem_barriers")); }
     b.push_back(let("tmem_base", "0", true));
+    if (c.clc) {
+        // the scheduler's ring: the roles walk `sched_ring` instead of stepping by a fixed stride
+        for (const char* bar : {"sched_full_bar", "sched_empty_bar", "clc_bar"}) b.push_back(let(bar, "smem_barriers"));
+        b.push_back(let("clc_response", "smem_barriers"));
+        b.push_back(let("sched_ring", "smem_barriers"));
+    }
 
     // barrier set-up by one thread, then the TMEM allocation by the MMA warp
     int epi_warps_per_buffer = nvfp4 ? 8 : 4;
@@ -155,6 +164,10 @@ Program lower(const KernelConfig& c, const tesserae_kernel_spec& ks) {
     if (nvfp4)
         init.push_back(forr("s", "0", stages, "1", {barrier(OpKind::MbarInit, "sf_full_bar", "", 1),
                                                     barrier(OpKind::MbarInit, "sf_ready_bar", "", 4 * c.cta_group)}));
+    if (c.clc)
+        init.push_back(forr("j", "0", "4", "1", {barrier(OpKind::MbarInit, "sched_full_bar", "", 1),
+                                                 barrier(OpKind::MbarInit, "sched_empty_bar", "", c.cta_group + 1 + 4 * c.cta_group)}));
+    if (c.clc) init.push_back(barrier(OpKind::MbarInit, "clc_bar", "", 1));
     b.push_back(iff("warp_id == 0 && lane == 0", init));
     if (pair) { b.push_back(barrier(OpKind::ClusterArrive)); b.push_back(barrier(OpKind::ClusterWait)); }
     Op alloc = mk(OpKind::TmemAlloc); alloc.var = "tmem_base"; alloc.imm = 512; alloc.sub = "cta_group::" + std::to_string(c.cta_group);
@@ -164,6 +177,14 @@ Program lower(const KernelConfig& c, const tesserae_kernel_spec& ks) {
     if (pair) { b.push_back(barrier(OpKind::ClusterArrive)); b.push_back(barrier(OpKind::ClusterWait)); } else b.push_back(barrier(OpKind::CtaSync));
     b.push_back(barrier(OpKind::Tcgen05FenceAfter));
 
+    // With the launch-control scheduler a role ends every tile by taking the next ring entry: bounded wait for the
+    // entry, then its hand-back on the leader CTA's barrier.
+    auto take_next = [&](std::vector<Stmt>& tile) {
+        if (!c.clc) return;
+        tile.push_back(wait("sched_full_bar", "(taken / 4) % 2", "TIMEOUT_SCHED"));
+        tile.push_back(barrier(OpKind::MbarArrive, "sched_empty_bar", "", 0, "", true));
+        tile.push_back(assign("taken", "taken + 1"));
+    };
     // ---- producer: one lane walks tiles x K blocks, waits for a free stage, arms the byte count, issues the loads
     {
         std::vector<Stmt> kloop = {
@@ -178,8 +199,10 @@ Program lower(const KernelConfig& c, const tesserae_kernel_spec& ks) {
         kloop.push_back(copy(pair ? "TmaPair" : "TmaLoad", "A", "smem_A", "full_bar"));
         kloop.push_back(copy(pair ? "TmaPair" : "TmaLoad", "B", "smem_B", "full_bar"));
         kloop.push_back(assign("it", "it + 1"));
-        std::vector<Stmt> body = {let("it", "0", true),
-                                  forr("t", "first_tile", "num_tiles", "tile_step", {forr("kb", "0", "num_k_blocks", "1", kloop)})};
+        std::vector<Stmt> ptile = {forr("kb", "0", "num_k_blocks", "1", kloop)};
+        take_next(ptile);
+        std::vector<Stmt> body = {let("it", "0", true), let("taken", "0", true),
+                                  forr("t", "first_tile", "num_tiles", "tile_step", ptile)};
         b.push_back(group(spec::Producer, {iff("lane == 0", body)}));
     }
     // ---- consumer: the MMA issuer (leader CTA of a pair); the whole warp waits, one elected lane issues
@@ -205,8 +228,9 @@ Program lower(const KernelConfig& c, const tesserae_kernel_spec& ks) {
         tile.push_back(forr("kb", "0", "num_k_blocks", "1", kloop));
         if (!fp8blk) tile.push_back(opstmt(acc_done));
         tile.push_back(assign("tile_iter", "tile_iter + 1"));
+        take_next(tile);
         b.push_back(group(spec::Consumer, {iff(pair ? "cta_rank == 0" : "1",
-                                               {let("it", "0", true), let("tile_iter", "0", true),
+                                               {let("it", "0", true), let("tile_iter", "0", true), let("taken", "0", true),
                                                 forr("t", "first_tile", "num_tiles", "tile_step", tile)})}));
     }
     // ---- scale warps (NVFP4): shared memory -> registers -> tensor memory, one warp per 32-lane quarter
@@ -248,8 +272,26 @@ Program lower(const KernelConfig& c, const tesserae_kernel_spec& ks) {
         tile.push_back(iff("lane == 0", {copy(c.scatter == 2 ? "TmaReduceAdd" : "TmaStore", "smem_C", "C"), barrier(OpKind::BulkCommit)}));
         if (!fp8blk) { tile.push_back(barrier(OpKind::Tcgen05FenceBefore)); tile.push_back(barrier(OpKind::WarpSync)); tile.push_back(release); }
         tile.push_back(assign("tile_iter", "tile_iter + 1"));
-        const std::string who = fp8blk ? "warp_id >= 4" : nvfp4 ? "warp_id >= 2 && warp_id < 10" : "warp_id >= 2";
-        b.push_back(group(spec::Epilogue, {iff(who, {let("tile_iter", "0", true), forr("t", "first_tile", "num_tiles", "tile_step", tile)})}));
+        take_next(tile);
+        const std::string who = fp8blk ? "warp_id >= 4" : nvfp4 ? "warp_id >= 2 && warp_id < 10" : c.clc ? "warp_id >= 2 && warp_id < 6" : "warp_id >= 2";
+        b.push_back(group(spec::Epilogue, {iff(who, {let("tile_iter", "0", true), let("taken", "0", true),
+                                                     forr("t", "first_tile", "num_tiles", "tile_step", tile)})}));
+    }
+    // ---- scheduler (cluster launch control): one lane of the leader CTA's last warp cancels clusters that have not
+    // started and feeds their tile ids to both CTAs of the pair
+    if (c.clc) {
+        Op tc = mk(OpKind::ClcTryCancel); tc.var = "clc_bar"; tc.expr = "clc_response";
+        Op q = mk(OpKind::ClcQuery); q.vars = {"cancelled", "next_tile"}; q.expr = "clc_response";
+        std::vector<Stmt> loop = {wait("sched_empty_bar", "((j / 4) % 2) ^ 1", "TIMEOUT_SCHED"),
+                                  barrier(OpKind::MbarArriveExpect, "clc_bar", "16"), opstmt(tc),
+                                  wait("clc_bar", "j % 2", "TIMEOUT_SCHED"),
+                                  let("cancelled", "0", true), let("next_tile", "0", true), opstmt(q)};
+        for (int r = 0; r < c.cta_group; ++r) {
+            Op st = mk(OpKind::StoreCluster); st.var = "next_tile"; st.expr = "sched_ring + j % 4"; st.imm = r;
+            loop.push_back(opstmt(st));
+            loop.push_back(barrier(OpKind::MbarArrive, "sched_full_bar", "", 0, "", true));
+        }
+        b.push_back(group(spec::Scheduler, {iff("cta_rank == 0 && lane == 0", {forr("j", "0", "num_tiles", "1", loop)})}));
     }
     // ---- teardown
     b.push_back(barrier(OpKind::Tcgen05FenceBefore));
@@ -328,6 +370,11 @@ struct Checker {
                 check_expr(scope, o.expr); break;
             case OpKind::TmemCommit: need_var(scope, o.var, "mbar '" + o.var + "' in TmemCommit"); break;
             case OpKind::SmemDescInit: need_var(scope, o.var, "desc var '" + o.var + "'"); check_expr(scope, o.expr); break;
+            case OpKind::ClcTryCancel: need_var(scope, o.var, "mbar '" + o.var + "' in ClcTryCancel"); check_expr(scope, o.expr); break;
+            case OpKind::ClcQuery:
+                for (auto& v : o.vars) need_var(scope, v, "variable '" + v + "' in ClcQuery");
+                check_expr(scope, o.expr); break;
+            case OpKind::StoreCluster: need_var(scope, o.var, "variable '" + o.var + "' in StoreCluster"); check_expr(scope, o.expr); break;
             case OpKind::ScaleFma: case OpKind::StoreShared:
                 for (auto& v : o.vars) need_var(scope, v, "variable '" + v + "'");
                 check_expr(scope, o.expr); break;

@@ -45,6 +45,9 @@ enum class OpKind {
     SmemDescInit,        // var = descriptor, expr = pointer, imm = swizzle B
     ScaleFma,            // vars = {accumulators, partial, scale}: acc += partial * scale (fp32 promotion)
     StoreShared,         // vars = source registers, expr = address
+    ClcTryCancel,        // var = mbar the 16-byte answer completes, expr = answer's address (cluster launch control)
+    ClcQuery,            // vars = {cancelled, tile}: reads the answer at expr
+    StoreCluster,        // var = value, expr = address in a CTA of the cluster (st.shared::cluster), imm = CTA rank
 };
 
 struct Op {
@@ -107,6 +110,9 @@ bool parse(const std::string& text, Program* out, std::string* err);
 // its origin spec selects): emission specialises that mainloop and carries the IR listing in the source header.
 // Returns 0 or a TESSERAE_LOWER_* code with *msg set.
 int emit(const Program& p, BackendOutput* out, std::string* msg);
+
+// The operation kind with this name in the text form, or -1.
+int op_kind_from_name(const std::string& name);
 
 // Number of operations of one kind anywhere in the program (for tests and hosts that inspect structure).
 int count_ops(const Program& p, OpKind kind);

@@ -264,3 +264,49 @@ def test_grouped_argument_errors(torch_cuda):
         grouped.run(a, a, c, bias, 1.0, 128, 128, 64)
     with pytest.raises(api.TesseraeError, match="grouped = 1"):
         plan_for(2, api.BF16, 1).run_grouped([(a, a, c, bias, 128, 128, 64)], ws, 4096)
+
+
+@pytest.mark.parametrize("cg", [1, 2])
+def test_launch_control_scheduler_equals_static_order(torch_cuda, cg):
+    """Tile order by cluster launch control (one cluster per tile; running clusters cancel and take over the ones that
+    have not started): every tile is computed exactly once, by the same arithmetic, so the result is bit-equal to the
+    static order's.  Shapes from one tile to many times the number of resident clusters."""
+    torch = torch_cuda
+    dyn = api.GemmPlan(api.KernelSpec(name=f"gemm_bf16_cg{cg}_bf16_b1_clc", elem=api.BF16, tile=(128, 256, 64), cta_group=cg,
+                                      out_elem=api.BF16, has_bias=1, tuning="CLC=1"))
+    static = plan_for(cg, api.BF16, 1)
+    for i, (m, n, k) in enumerate([(128, 256, 64), (200, 264, 72), (1000, 1016, 1032), (4096, 4096, 256), (8192, 2048, 512),
+                                   (8192, 8192, 128)]):
+        p = O.make_bf16_problem(m, n, k, seed=800 + i, with_bias=True)
+        got = run_gpu(torch, dyn, p, m, n, k, api.BF16, alpha=0.75)
+        want = run_gpu(torch, static, p, m, n, k, api.BF16, alpha=0.75)
+        assert not np.isnan(got).any(), (cg, m, n, k)
+        assert np.array_equal(got, want), (cg, m, n, k)
+    for _ in range(3):                                    # back-to-back launches: every launch has its own grid to cancel from
+        got = run_gpu(torch, dyn, p, m, n, k, api.BF16, alpha=0.75)
+        assert np.array_equal(got, want)
+
+
+def test_grouped_launch_with_launch_control(torch_cuda):
+    """Grouped problems of very different K under the dynamic order: bit-equal to one static launch per problem."""
+    torch = torch_cuda
+    spec = dict(elem=api.BF16, tile=(128, 256, 64), cta_group=2, out_elem=api.BF16, has_bias=1)
+    grouped = api.GemmPlan(api.KernelSpec(name="gemm_bf16_cg2_bf16_grouped_clc", grouped=1, tuning="CLC=1", **spec))
+    single = plan_for(2, api.BF16, 1)
+    st = torch.cuda.current_stream().cuda_stream
+    shapes = [(512, 1024, 64), (512, 1024, 4096), (300, 520, 256), (1024, 2048, 1024), (256, 256, 8192), (2048, 1024, 128)] * 3
+    keep, problems, singles = [], [], []
+    for i, (m, n, k) in enumerate(shapes):
+        p = O.make_bf16_problem(m, n, k, seed=850 + i, with_bias=True)
+        a, b, bias = to_dev(torch, p["a_bits"]), to_dev(torch, p["b_bits"]), to_dev(torch, p["bias_bits"])
+        c = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+        c1 = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+        single.run(a, b, c1, bias, 1.0, m, n, k, stream=st)
+        keep.append((a, b, bias, c)); problems.append((a, b, c, bias, m, n, k)); singles.append(c1)
+    nbytes = api.grouped_workspace_bytes(len(problems))
+    ws = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    grouped.run_grouped(problems, ws, nbytes, stream=st)
+    torch.cuda.synchronize()
+    assert grouped.status() == 0 and single.status() == 0
+    for (m, n, k), (_, _, _, c), c1 in zip(shapes, keep, singles):
+        assert torch.equal(c.view(torch.int16), c1.view(torch.int16)), (m, n, k)

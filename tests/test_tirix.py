@@ -13,6 +13,10 @@ SPECS = {
     "scatter_add": api.KernelSpec(name="gemm_scatter_add", elem=api.BF16, tile=(128, 256, 64), out_elem=api.F32, scatter=2),
     "fp8_block": api.KernelSpec(name="gemm_fp8blk", elem=api.F8E4M3, tile=(128, 256, 128), out_elem=api.BF16, scale_mode=api.SCALE_FP8_BLOCK),
     "nvfp4": api.KernelSpec(name="gemm_nvfp4", elem=api.F4E2M1, tile=(128, 256, 256), out_elem=api.BF16, scale_mode=api.SCALE_NVFP4),
+    "grouped": api.KernelSpec(name="gemm_grouped", elem=api.BF16, tile=(128, 256, 64), out_elem=api.BF16, has_bias=1, grouped=1),
+    "clc": api.KernelSpec(name="gemm_clc", elem=api.BF16, tile=(128, 256, 64), out_elem=api.BF16, has_bias=1, tuning="CLC=1"),
+    "fp8_tail": api.KernelSpec(name="gemm_fp8blk_tail", elem=api.F8E4M3, tile=(128, 256, 128), out_elem=api.BF16,
+                               scale_mode=api.SCALE_FP8_BLOCK, tuning="TAIL_SPLITS=8"),
 }
 
 
@@ -48,6 +52,23 @@ def test_structure_follows_the_spec():
     assert "sub=TmaReduceAdd tensors=smem_C,C" in api.Tirix.lower(SPECS["scatter_add"]).text()
     # smem ring as Desc_to_tirix states it: (depth, rows, K extent), here with the stage count the smem fit gives
     assert "tensor smem_A space=1 elem=1 swizzle=3 shape=6,128,128 stride=16384,128,1" in text
+
+
+def test_scheduler_role_of_the_launch_control_variant():
+    """Cluster's Scheduler role (lib/pipeline/cluster.mli:17-21): present only when the spec asks for launch control;
+    then the kernel has a seventh warp, the ring's barriers, and every role takes its next tile from the ring."""
+    static, clc = api.Tirix.lower(SPECS["bf16"]), api.Tirix.lower(SPECS["clc"])
+    assert "warpgroup Scheduler" not in static.text() and static.count_ops("ClcTryCancel") == 0
+    text = clc.text()
+    assert "warpgroup Scheduler" in text
+    assert clc.count_ops("ClcTryCancel") == 1 and clc.count_ops("ClcQuery") == 1 and clc.count_ops("StoreCluster") == 2
+    assert "op MbarInit var=sched_empty_bar imm=11" in text          # 2 producer lanes + the MMA warp + 8 epilogue warps of the pair
+    assert text.count("sub=TIMEOUT_SCHED") == 5                      # producer, MMA issuer, epilogue, and the scheduler's two waits
+    src = api.backend_emit(SPECS["clc"])
+    assert "#define TS_CLC 1" in src.includes and "clusterlaunchcontrol.try_cancel" in src.full_source
+    assert "block=224 threads" in src.full_source and "block=192 threads" in api.backend_emit(SPECS["bf16"]).full_source
+    with pytest.raises(api.TesseraeError, match="launch-control scheduler is for the unscaled kernels"):
+        api.backend_emit(api.KernelSpec(name="k", elem=api.F8E4M3, tile=(128, 256, 128), scale_mode=api.SCALE_FP8_BLOCK, tuning="CLC=1"))
 
 
 def _edit(text: str, old: str, new: str) -> api.Tirix:
