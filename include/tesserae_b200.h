@@ -408,7 +408,11 @@ int tesserae_tensor_map_2d(void* out_map128, int elem, const void* gptr, uint64_
 
 /* ------------------------------------------------------------------ GEMM plans and Runtime.run */
 typedef struct tesserae_gemm_plan tesserae_gemm_plan;
-/* Emit + compile (cached) + load the kernel a spec names.  One plan serves any M, N, K. */
+/* Emit + compile (cached) + load the kernel a spec names.  One plan serves any M, N, K.
+ * A plan belongs to the device that was current when it was made (calls with another device current are refused).
+ * Calls on one plan may come from any host thread but not from two at once: the plan holds per-call host state (the
+ * status word's owner, the pinned staging copy of a grouped launch's problem table, the host-buffer entry points'
+ * workspaces).  Different plans are independent. */
 int tesserae_gemm_plan_create(const tesserae_kernel_spec* spec, tesserae_gemm_plan** plan);
 void tesserae_gemm_plan_destroy(tesserae_gemm_plan* plan);
 int tesserae_gemm_plan_info(const tesserae_gemm_plan* plan, int* cta_group, int* block_n, int* stages,

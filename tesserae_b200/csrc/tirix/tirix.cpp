@@ -95,12 +95,10 @@ Program lower(const KernelConfig& c, const tesserae_kernel_spec& ks) {
     if (c.scatter) { p.params.push_back({"rows_per_owner", false}); p.params.push_back({"m_rotate", false}); }
     if (fp8blk) { p.params.push_back({"WS_tmap", true}); p.params.push_back({"scale_a", false}); p.params.push_back({"scale_b", false}); }
     if (nvfp4) { p.params.push_back({"SFA_tmap", true}); p.params.push_back({"SFB_tmap", true}); }
-    for (const char* n : {"bias", "alpha", "M", "N", "K", "group_m"}) p.params.push_back({n, false});
+    if (c.grouped) p.params.push_back({"alpha", false});
+    else for (const char* n : {"bias", "alpha", "M", "N", "K", "group_m"}) p.params.push_back({n, false});
     if (fp8blk) { p.params.push_back({"full_tiles", false}); p.params.push_back({"tail_splits", false}); }
     p.params.push_back({"status", false});
-    // (a grouped kernel reads the three maps from the table row of the tile it is on; they are named here so that
-    // the operations below can refer to them)
-    if (c.grouped) p.params.push_back({"A_tmap", true}), p.params.push_back({"B_tmap", true}), p.params.push_back({"C_tmap", true});
 
     // Tensors: global operands, the shared-memory ring (depth, rows, bytes of K : row-major inside a stage, the
     // layout the reference states column-major, lib/tirix/desc_to_tirix.ml:66-85), tensor memory, output staging.
@@ -130,6 +128,10 @@ Program lower(const KernelConfig& c, const tesserae_kernel_spec& ks) {
     const long long stage_bytes = (128LL + load_n) * row_bytes * c.cta_group;
 
     std::vector<Stmt>& b = p.body;
+    if (c.grouped) {
+        // a grouped kernel reads its maps and sizes from the table row of the tile it is on
+        for (const char* n : {"A_tmap", "B_tmap", "C_tmap", "bias", "M", "N", "K", "group_m"}) b.push_back(let(n, "problem_table"));
+    }
     b.push_back(let("warp_id", "threadIdx.x / 32"));
     b.push_back(let("lane", "threadIdx.x % 32"));
     b.push_back(let("cta_rank", pair ? "cluster_ctarank" : "0"));
