@@ -187,8 +187,11 @@ int derive_config(const tesserae_kernel_spec& ks, KernelConfig* cfg, std::string
         }
     }
     const int chunk = (c.out_elem == TESSERAE_F32) ? 32 : 64;
-    if (c.block_n < 16 * c.cta_group || c.block_n > 256 || c.block_n % (16 * c.cta_group) != 0 || c.block_n % chunk != 0) {
-        if (msg) *msg = "IncompatibleTile: tile.n must be a multiple of " + std::to_string(std::max(chunk, 16 * c.cta_group)) + " and <= 256";
+    // 512 columns: the unscaled CTA-pair kernels only (two MMA groups of 256 into one accumulator that fills tensor memory)
+    const bool wide = c.block_n == 512 && c.cta_group == 2 && ks.scale_mode == TESSERAE_SCALE_NONE;
+    if (!wide && (c.block_n < 16 * c.cta_group || c.block_n > 256 || c.block_n % (16 * c.cta_group) != 0 || c.block_n % chunk != 0)) {
+        if (msg) *msg = "IncompatibleTile: tile.n must be a multiple of " + std::to_string(std::max(chunk, 16 * c.cta_group)) +
+                        " and <= 256 (512 for an unscaled CTA-pair kernel)";
         return spec::IncompatibleTile;
     }
     if (ks.scale_mode == TESSERAE_SCALE_FP8_BLOCK && ks.elem != TESSERAE_F8E4M3) {
@@ -200,7 +203,7 @@ int derive_config(const tesserae_kernel_spec& ks, KernelConfig* cfg, std::string
         return spec::UnsupportedElem;
     }
 
-    c.b_box_rows = c.block_n / c.cta_group;
+    c.b_box_rows = (c.block_n > 256 ? 256 : c.block_n) / c.cta_group;      // one TMA load per MMA group of at most 256 columns
     if (c.scale_mode == TESSERAE_SCALE_FP8_BLOCK) {
         // Promotion warps on top of the producer and MMA warps.  8 (two per scheduler) measured
         // faster than 16 on the 256-wide tile: the TMEM reads contend with the running MMA, not with

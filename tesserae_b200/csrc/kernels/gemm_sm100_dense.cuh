@@ -96,7 +96,16 @@ namespace ts_dense {
 constexpr ts_u32 kBlockM      = 128;                          // rows per CTA
 constexpr ts_u32 kTileM       = kBlockM * TS_CTA_GROUP;       // rows per MMA tile
 constexpr ts_u32 kBlockN      = TS_BLOCK_N;
+// One MMA instruction is at most 256 columns wide.  A 512-wide tile (CTA pairs only) is two MMA groups per K step,
+// each into its own 256 columns of tensor memory: it streams (128 + 256) rows of operands per 1024 tensor cycles and
+// CTA, 48 bytes per clock from L2 where the 256-wide tile needs 64 -- and 64 is what an SM can take, so the narrower
+// tile runs at the supply limit (measured: with a quarter of the operand loads left out it is 15 % faster).  The
+// price is one accumulator instead of two: the epilogue hands the halves back one by one, and the next tile's MMAs
+// wait for them.
+constexpr ts_u32 kMmaN        = kBlockN > 256 ? 256 : kBlockN;
+constexpr ts_u32 kHalves      = kBlockN / kMmaN;              // MMA groups per K step
 constexpr ts_u32 kLoadN       = kBlockN / TS_CTA_GROUP;       // B rows this CTA loads
+constexpr ts_u32 kHalfRows    = kMmaN / TS_CTA_GROUP;         // of which one MMA group reads this many
 constexpr ts_u32 kBlockKBytes = 16u << TS_SWIZZLE_B;          // one swizzle row: 32, 64 or 128 bytes of K
 constexpr ts_u32 kBlockK      = kBlockKBytes / TS_ELEM_BYTES; // K elements per stage
 constexpr ts_u32 kUmmaKBytes  = 32;                           // K bytes per MMA instruction
@@ -105,7 +114,7 @@ constexpr ts_u32 kStages      = TS_STAGES;
 constexpr ts_u32 kSmemA       = kBlockM * kBlockKBytes;       // 16384
 constexpr ts_u32 kSmemB       = kLoadN * kBlockKBytes;
 constexpr ts_u32 kStageBytes  = kSmemA + kSmemB;
-constexpr ts_u32 kNumAcc      = 2;                            // TMEM accumulator buffers
+constexpr ts_u32 kNumAcc      = 2 * kBlockN <= 512 ? 2 : 1;   // TMEM accumulator buffers
 constexpr ts_u32 kTmemCols    = (kNumAcc * kBlockN <= 32) ? 32 : (kNumAcc * kBlockN <= 64) ? 64 :
                                 (kNumAcc * kBlockN <= 128) ? 128 : (kNumAcc * kBlockN <= 256) ? 256 : 512;
 constexpr ts_u32 kOutBytes    = TS_OUT_F32 ? 4 : 2;
@@ -119,14 +128,16 @@ constexpr ts_u32 kNumEpiWarps = 4;
 constexpr ts_u32 kStoreBufs   = TS_STORE_BUFS;                // staging buffers per epilogue warp (stores in flight + 1)
 constexpr ts_u32 kSmemC       = kNumEpiWarps * kStoreBufs * kStoreBuf;
 constexpr ts_u32 kSchedRing   = 4;                            // tile ids in flight between the scheduler warp and the roles
-constexpr ts_u32 kNumBars     = 2 * kStages + 2 * kNumAcc + (TS_CLC ? 2 * kSchedRing + 1 : 0);
+constexpr ts_u32 kNumBars     = 2 * kStages + kNumAcc + kNumAcc * kHalves + (TS_CLC ? 2 * kSchedRing + 1 : 0);
 constexpr ts_u32 kSmemTotal   = kStages * kStageBytes + kSmemC + kNumBars * 8 + 16 + (TS_CLC ? 48 : 0);
 constexpr ts_u32 kThreads     = 192 + (TS_CLC ? 32 : 0);      // producer, MMA issuer, four epilogue warps (+ scheduler)
 constexpr ts_u32 kNoTile      = 0xffffffffu;
 // Arrivals that hand a ring entry back: the producer lane of each CTA, the MMA warp (leader only), the epilogue warps.
 constexpr ts_u32 kSchedReaders = TS_CTA_GROUP + 1 + kNumEpiWarps * TS_CTA_GROUP;
 
-static_assert(kBlockN % (16 * TS_CTA_GROUP) == 0 && kBlockN >= 16 * TS_CTA_GROUP && kBlockN <= 256, "bad TS_BLOCK_N");
+static_assert(kBlockN % (16 * TS_CTA_GROUP) == 0 && kBlockN >= 16 * TS_CTA_GROUP && (kBlockN <= 256 || (kBlockN == 512 && TS_CTA_GROUP == 2)),
+              "bad TS_BLOCK_N");
+static_assert(kNumChunks % kHalves == 0, "a store chunk must not straddle two MMA groups");
 static_assert(kBlockN % kChunkCols == 0, "TS_BLOCK_N must be a multiple of the store chunk");
 static_assert(kNumAcc * kBlockN <= 512, "accumulators exceed tensor memory");
 static_assert(kSmemTotal + 1024 <= 232448, "shared memory over the 227 KB limit");
@@ -185,16 +196,16 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
     const ts_u32 full_bar       = bar_base;                       // [kStages]
     const ts_u32 empty_bar      = full_bar + 8 * kStages;         // [kStages]
     const ts_u32 tmem_full_bar  = empty_bar + 8 * kStages;        // [kNumAcc]
-    const ts_u32 tmem_empty_bar = tmem_full_bar + 8 * kNumAcc;    // [kNumAcc]
+    const ts_u32 tmem_empty_bar = tmem_full_bar + 8 * kNumAcc;    // [kNumAcc][kHalves]
 #if TS_CLC
-    const ts_u32 sched_full     = tmem_empty_bar + 8 * kNumAcc;   // [kSchedRing] entry j holds a tile id
+    const ts_u32 sched_full     = tmem_empty_bar + 8 * kNumAcc * kHalves;   // [kSchedRing] entry j holds a tile id
     const ts_u32 sched_empty    = sched_full + 8 * kSchedRing;    // [kSchedRing] every role of the pair has read it (leader CTA's)
     const ts_u32 clc_bar        = sched_empty + 8 * kSchedRing;   // the launch control's answer has landed
     const ts_u32 tmem_ptr_smem  = clc_bar + 8;                    // u32
     const ts_u32 clc_response   = (tmem_ptr_smem + 4 + 15u) & ~15u;   // 16 bytes
     const ts_u32 sched_ring     = clc_response + 16;              // [kSchedRing] u32
 #else
-    const ts_u32 tmem_ptr_smem  = tmem_empty_bar + 8 * kNumAcc;   // u32
+    const ts_u32 tmem_ptr_smem  = tmem_empty_bar + 8 * kNumAcc * kHalves;   // u32
 #endif
 
     const ts_u32 warp_id  = threadIdx.x >> 5;
@@ -236,10 +247,9 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
             ts_mbar_init(full_bar + 8 * s, 1);    // producer's arrive.expect_tx (leader CTA)
             ts_mbar_init(empty_bar + 8 * s, 1);   // one tcgen05.commit
         }
-        for (ts_u32 b = 0; b < kNumAcc; ++b) {
-            ts_mbar_init(tmem_full_bar + 8 * b, 1);                               // one tcgen05.commit
-            ts_mbar_init(tmem_empty_bar + 8 * b, kNumEpiWarps * TS_CTA_GROUP);    // one arrive per epilogue warp
-        }
+        for (ts_u32 b = 0; b < kNumAcc; ++b) ts_mbar_init(tmem_full_bar + 8 * b, 1);          // one tcgen05.commit
+        for (ts_u32 b = 0; b < kNumAcc * kHalves; ++b)
+            ts_mbar_init(tmem_empty_bar + 8 * b, kNumEpiWarps * TS_CTA_GROUP);               // one arrive per epilogue warp
 #if TS_CLC
         for (ts_u32 j = 0; j < kSchedRing; ++j) {
             ts_mbar_init(sched_full + 8 * j, 1);                 // the scheduler's arrive (one per CTA, on that CTA's barrier)
@@ -307,7 +317,7 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
                 m_blk = (m_blk + (ts_u32)m_rotate) % num_m;
 #endif
                 const int a_row = (int)(m_blk * kTileM + cta_rank * kBlockM);
-                const int b_row = (int)(n_blk * kBlockN + cta_rank * kLoadN);
+                const int b_row = (int)(n_blk * kBlockN + cta_rank * kHalfRows);    // + h * kMmaN for MMA group h
                 for (ts_u32 kb = 0; kb < ti.num_k_blocks; ++kb, ++it) {
                     const ts_u32 s = it % kStages;
                     const ts_u32 ph = (it / kStages) & 1u;
@@ -318,12 +328,15 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
                     if (TS_CTA_GROUP == 1) {
                         ts_mbar_arrive_expect_tx(full_bar + 8 * s, kStageBytes);
                         ts_tma_load_2d(smem_a + s * kSmemA, ti.a, full_bar + 8 * s, kc, a_row);
-                        ts_tma_load_2d(smem_b + s * kSmemB, ti.b, full_bar + 8 * s, kc, b_row);
+                        ts_tma_load_2d(smem_b + s * kSmemB, ti.b, full_bar + 8 * s, kc, b_row);     // (one MMA group: kHalves is 1)
                     } else {
                         const ts_u32 leader_full = ts_mapa(full_bar + 8 * s, 0);
                         if (is_leader) ts_mbar_arrive_expect_tx(full_bar + 8 * s, kStageBytes * 2);
                         ts_tma_load_2d_pair(smem_a + s * kSmemA, ti.a, leader_full, kc, a_row);
-                        ts_tma_load_2d_pair(smem_b + s * kSmemB, ti.b, leader_full, kc, b_row);
+#pragma unroll
+                        for (ts_u32 h = 0; h < kHalves; ++h)      // this CTA's rows of B for each MMA group, one after the other
+                            ts_tma_load_2d_pair(smem_b + s * kSmemB + h * kHalfRows * kBlockKBytes, ti.b, leader_full, kc,
+                                                b_row + (int)(h * kMmaN));
                     }
                 }
             }
@@ -333,7 +346,7 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
         // ------------------------------------------------------------ MMA issuer
         // The whole warp walks the loop (and waits on the barriers); one elected lane issues.
         if (is_leader) {
-            constexpr ts_u32 idesc = ts_idesc_dense(TS_AB_FMT, TS_AB_FMT, kTileM, kBlockN, TS_MMA_KIND == TS_KIND_I8 ? 2u : 1u);
+            constexpr ts_u32 idesc = ts_idesc_dense(TS_AB_FMT, TS_AB_FMT, kTileM, kMmaN, TS_MMA_KIND == TS_KIND_I8 ? 2u : 1u);
             const bool elected = ts_elect_one();
             ts_u32 it = 0, tile_iter = 0;
             bool ok = true;
@@ -351,11 +364,7 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
 #endif
                 const ts_u32 acc = tile_iter % kNumAcc;
                 const ts_u32 acc_ph = (tile_iter / kNumAcc) & 1u;
-                if (!ts_mbar_wait(tmem_empty_bar + 8 * acc, acc_ph ^ 1u)) {
-                    if (elected) atomicOr(status, TS_ERR_TIMEOUT_TMEM_EMPTY);
-                    ok = false; break;
-                }
-                ts_tc_fence_after();
+                // (the accumulator's column groups are waited for one by one, each in front of its first MMA)
                 const ts_u32 d_tmem = tmem_base + acc * kBlockN;
                 for (ts_u32 kb = 0; kb < ti.num_k_blocks; ++kb, ++it) {
                     const ts_u32 s = it % kStages;
@@ -366,14 +375,28 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
                     }
                     ts_tc_fence_after();
                     const ts_u64 a_desc = ts_smem_desc_kmajor<TS_SWIZZLE_B>(smem_a + s * kSmemA);
-                    const ts_u64 b_desc = ts_smem_desc_kmajor<TS_SWIZZLE_B>(smem_b + s * kSmemB);
-                    if (elected) {
 #pragma unroll
-                        for (ts_u32 k = 0; k < kNumUmma; ++k) {
-                            // +32 bytes along K inside the swizzle row = +2 in the address field
-                            ts_umma<TS_CTA_GROUP, TS_MMA_KIND>(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc,
-                                                               (kb | k) != 0u);
+                    for (ts_u32 h = 0; h < kHalves; ++h) {
+                        if (kb == 0u) {
+                            // first MMA of this tile into column group h: the epilogue must have read the group out
+                            if (!ts_mbar_wait(tmem_empty_bar + 8 * (acc * kHalves + h), acc_ph ^ 1u)) {
+                                if (elected) atomicOr(status, TS_ERR_TIMEOUT_TMEM_EMPTY);
+                                ok = false; break;
+                            }
+                            ts_tc_fence_after();
                         }
+                        const ts_u64 b_desc = ts_smem_desc_kmajor<TS_SWIZZLE_B>(smem_b + s * kSmemB + h * kHalfRows * kBlockKBytes);
+                        if (elected) {
+#pragma unroll
+                            for (ts_u32 k = 0; k < kNumUmma; ++k) {
+                                // +32 bytes along K inside the swizzle row = +2 in the address field
+                                ts_umma<TS_CTA_GROUP, TS_MMA_KIND>(d_tmem + h * kMmaN, a_desc + 2 * k, b_desc + 2 * k, idesc,
+                                                                   (kb | k) != 0u);
+                            }
+                        }
+                    }
+                    if (!ok) break;
+                    if (elected) {
                         // frees the smem stage (in both CTAs of a pair) once these MMAs have read it
                         if (TS_CTA_GROUP == 1) ts_umma_commit<1>(empty_bar + 8 * s);
                         else                   ts_umma_commit_pair(empty_bar + 8 * s, 3);
@@ -497,13 +520,16 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
 #endif
                     ts_bulk_commit();   // committed even when empty so that "one group pending" always means the previous chunk
                 }
-            }
-            // every column of this accumulator buffer has been read: hand it back to the MMA issuer
-            ts_tc_fence_before();
-            __syncwarp();
-            if (lane == 0) {
-                if (TS_CTA_GROUP == 2) ts_mbar_arrive_cluster(leader_tmem_empty + 8 * acc);
-                else                   ts_mbar_arrive(tmem_empty_bar + 8 * acc);
+                if ((j + 1) % (kNumChunks / kHalves) == 0) {
+                    // every column of one MMA group of this accumulator has been read: hand the group back to the MMA issuer
+                    const ts_u32 grp = acc * kHalves + j / (kNumChunks / kHalves);
+                    ts_tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (TS_CTA_GROUP == 2) ts_mbar_arrive_cluster(leader_tmem_empty + 8 * grp);
+                        else                   ts_mbar_arrive(tmem_empty_bar + 8 * grp);
+                    }
+                }
             }
         }
         if (lane == 0) ts_bulk_wait_all();

@@ -60,6 +60,15 @@ def test_grouped_kernel_takes_a_problem_table():
     assert api.grouped_workspace_bytes(3) == 4 * 448 and api.grouped_workspace_bytes(0) == 0
 
 
+def test_wide_tile_is_for_unscaled_cta_pairs():
+    wide = api.backend_emit(api.KernelSpec(name="k", tile=(128, 512, 64), cta_group=2, out_elem=api.BF16))
+    assert "#define TS_BLOCK_N 512" in wide.includes and "#define TS_STAGES 4" in wide.includes
+    with pytest.raises(api.TesseraeError, match="512 for an unscaled CTA-pair kernel"):
+        api.backend_emit(api.KernelSpec(name="k", tile=(128, 512, 64), cta_group=1))
+    with pytest.raises(api.TesseraeError, match="512 for an unscaled CTA-pair kernel"):
+        api.backend_emit(api.KernelSpec(name="k", elem=api.F8E4M3, tile=(128, 512, 128), scale_mode=api.SCALE_FP8_BLOCK))
+
+
 def test_operand_swizzle_follows_the_tile():
     """Swizzle.smem_selector (lib/core/swizzle.ml:46-56) decides the operand tiles' swizzle from tile.k; the
     emitted kernel is specialised on that B, it is not a constant of the backend."""

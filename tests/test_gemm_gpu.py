@@ -310,3 +310,21 @@ def test_grouped_launch_with_launch_control(torch_cuda):
     assert grouped.status() == 0 and single.status() == 0
     for (m, n, k), (_, _, _, c), c1 in zip(shapes, keep, singles):
         assert torch.equal(c.view(torch.int16), c1.view(torch.int16)), (m, n, k)
+
+
+@pytest.mark.parametrize("out_elem,bias,tuning", [(api.BF16, 1, ""), (api.F32, 0, ""), (api.BF16, 1, "CLC=1")])
+def test_wide_tile_equals_narrow(torch_cuda, out_elem, bias, tuning):
+    """The 512-column tile of the CTA-pair kernel (two MMA groups of 256 columns into one accumulator that fills tensor
+    memory, handed back to the MMA issuer group by group): every output element is the same sum over K in the same
+    order as with the 256-column tile, so the results are bit-equal."""
+    torch = torch_cuda
+    wide = api.GemmPlan(api.KernelSpec(name=f"gemm_bf16_cg2_n512_o{out_elem}_b{bias}{tuning.replace('=', '')}", elem=api.BF16,
+                                       tile=(128, 512, 64), cta_group=2, out_elem=out_elem, has_bias=bias, tuning=tuning))
+    narrow = plan_for(2, out_elem, bias)
+    for i, (m, n, k) in enumerate([(256, 512, 64), (200, 264, 72), (1000, 1016, 1032), (300, 1544, 520), (4096, 4096, 256),
+                                   (8192, 1024, 128)]):
+        p = O.make_bf16_problem(m, n, k, seed=870 + i, with_bias=bool(bias))
+        got = run_gpu(torch, wide, p, m, n, k, out_elem, alpha=0.75)
+        want = run_gpu(torch, narrow, p, m, n, k, out_elem, alpha=0.75)
+        assert not np.isnan(got).any(), (m, n, k)
+        assert np.array_equal(got, want), (m, n, k)
