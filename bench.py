@@ -55,9 +55,10 @@ WORKLOADS = {
                         bias=False, out="bf16", shard="k_strong", tile="256x256x64 per CTA pair"),
 }
 SUB_CONFIGS = ["fp8_block", "nvfp4", "bf16_ksplit"]
+BF16_TILE_N = 512       # columns of the CTA-pair tile of the bf16 workloads (the kernels also take 256)
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel, from the ncu
 # captures summarised under profiles/; None where no capture exists.
-TRAFFIC_BYTES = {"bf16_8192_bias": 1.2138e9, "fp8_block": 3.291e8, "nvfp4": 1.5667e9}
+TRAFFIC_BYTES = {"bf16_8192_bias": 9.694e8, "fp8_block": 3.291e8, "nvfp4": 1.5667e9}
 
 
 def measured_peaks():
@@ -157,7 +158,7 @@ def run_reference(args, w, rank):
     line = {"impl": "reference", "metric": "gemm_tflops", "value": v, "unit": "TFLOP/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * sum(dt for _, dt in vals) / len(vals),
             "higher_is_better": True, "scaling": scaling_of(w), "vs_baseline": None, "dtype": w["dtype"],
-            "data": "synthetic", "config": workload_config(args.workload, w, args.gpus),
+            "data": "synthetic", "config": workload_config(args.workload, w, args.gpus, tile_n=args.tile_n),
             "cpu_baseline": dict(best, value=v),
             "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
@@ -167,7 +168,7 @@ def scaling_of(w):
     return "weak" if w["shard"] == "n_weak" else "strong"
 
 
-def workload_config(name, w, gpus, exchange="fused"):
+def workload_config(name, w, gpus, exchange="fused", tile_n=0):
     m, n, k = w["m"], w["n"], w["k"]
     if w["shard"] == "n_weak":
         sharding = "single GPU" if gpus == 1 else f"N-split over {gpus} GPUs ({n} columns each), no collective"
@@ -182,7 +183,8 @@ def workload_config(name, w, gpus, exchange="fused"):
                        else "fused into the GEMM's stores over NVLink peer memory, summed by the owner" if exchange == "fused"
                        else "by NCCL") + ", bf16 cast")
         shape = {"m": m, "n_total": n, "k_per_gpu": k // gpus, "k": k}
-    return dict({"workload": name, "tile": w["tile"], "sharding": sharding,
+    tile = w["tile"] if w["kind"] not in ("bf16", "ksplit") else f"256x{tile_n or BF16_TILE_N}x64 per CTA pair"
+    return dict({"workload": name, "tile": tile, "sharding": sharding,
                  "epilogue": "alpha=1" + (" + bf16 bias[n]" if w["bias"] else "") + f" -> {w['out']}",
                  "l2": "operands and output per GPU exceed the 126 MB L2"}, **shape)
 
@@ -191,8 +193,9 @@ def workload_config(name, w, gpus, exchange="fused"):
 class Workload:
     """Builds device + pinned host operands for this rank's shard; step() launches the hot path once."""
 
-    def __init__(self, name, w, rank, world, dev, exchange="fused", tuning=""):
+    def __init__(self, name, w, rank, world, dev, exchange="fused", tuning="", tile_n=0):
         self.exchange = exchange
+        self.tile_n = tile_n or BF16_TILE_N   # bf16 workloads: columns of the CTA-pair tile
         self.tuning = tuning          # the spec's tuning string ("NAME=VALUE;..."), for A/B runs from the command line
         import numpy as np
         import torch
@@ -230,9 +233,10 @@ class Workload:
         self.bias_host = self._pin(self.bias) if w["bias"] else None
         self.c_host = t.empty((self.m, self.n), dtype=t.bfloat16).pin_memory()
         self.c = t.empty((self.m, self.n), dtype=t.bfloat16, device=self.dev)
-        self.plan = api.GemmPlan(api.KernelSpec(name=f"gemm_bf16_cg2_bf16_b{int(w['bias'])}", elem=api.BF16,
-                                                tile=(128, 256, 64), cta_group=2, out_elem=api.BF16, has_bias=int(w["bias"]),
-                                                tuning=self.tuning))
+        tile_n = self.tile_n
+        self.plan = api.GemmPlan(api.KernelSpec(name=f"gemm_bf16_cg2_bf16_b{int(w['bias'])}" + ("" if tile_n == 256 else f"_n{tile_n}"),
+                                                elem=api.BF16, tile=(128, tile_n, 64), cta_group=2, out_elem=api.BF16,
+                                                has_bias=int(w["bias"]), tuning=self.tuning))
         self.step = lambda: self.plan.run(self.a, self.b, self.c, self.bias, 1.0, self.m, self.n, self.k, stream=self.stream)
         self.e2e_step = lambda: self.plan.run_host(self.a_host, self.b_host, self.c_host, self.bias_host, 1.0,
                                                    self.m, self.n, self.k)
@@ -318,9 +322,11 @@ class Workload:
         self.c_host = t.empty((rows, self.n), dtype=t.bfloat16).pin_memory()
         fused = self.world > 1 and self.exchange == "fused"
         reduce_ = self.world > 1 and self.exchange == "reduce"
-        self.plan = api.GemmPlan(api.KernelSpec(name="gemm_bf16_cg2_f32_scatter" if fused else
-                                                "gemm_bf16_cg2_f32_scatter_add" if reduce_ else "gemm_bf16_cg2_f32_b0",
-                                                elem=api.BF16, tile=(128, 256, 64), cta_group=2, out_elem=api.F32,
+        tile_n = self.tile_n
+        self.plan = api.GemmPlan(api.KernelSpec(name=("gemm_bf16_cg2_f32_scatter" if fused else
+                                                      "gemm_bf16_cg2_f32_scatter_add" if reduce_ else "gemm_bf16_cg2_f32_b0")
+                                                + ("" if tile_n == 256 else f"_n{tile_n}"),
+                                                elem=api.BF16, tile=(128, tile_n, 64), cta_group=2, out_elem=api.F32,
                                                 scatter=1 if fused else 2 if reduce_ else 0))
         nbytes = self.partial.numel() * 4
         self.launches_per_step = 2
@@ -518,7 +524,8 @@ def measure(name, w, rank, local_rank, world, dev, args, exchange="fused", extra
     oracle check, reduces over the ranks (max) and returns the record (on every rank) plus the live workload."""
     import torch
     import torch.distributed as dist
-    wl = Workload(name, w, rank, world, dev, exchange=exchange, tuning=args.tuning if name == args.workload else "")
+    wl = Workload(name, w, rank, world, dev, exchange=exchange, tuning=args.tuning if name == args.workload else "",
+                  tile_n=args.tile_n)
 
     def sync_all():
         torch.cuda.synchronize()
@@ -593,7 +600,7 @@ def measure(name, w, rank, local_rank, world, dev, args, exchange="fused", extra
     nominal = NOMINAL_PEAK_TFLOPS[w["dtype"]]
     rec = {
         "value": value, "unit": "TFLOP/s", "ms_per_step": ms_per_step, "steps": args.steps, "warmup": args.warmup,
-        "scaling": scaling_of(w), "dtype": w["dtype"], "config": workload_config(name, w, world, exchange),
+        "scaling": scaling_of(w), "dtype": w["dtype"], "config": workload_config(name, w, world, exchange, tile_n=args.tile_n),
         "pct_of_nominal_dense_peak": 100.0 * value / world / nominal,
         "burst": {"value": flops_step / (burst * 1e-3) / 1e12, "unit": "TFLOP/s",
                   "note": "best of 10 single steps, each after an idle gap and two untimed steps",
@@ -692,6 +699,9 @@ def main():
     ap.add_argument("--sustained-seconds", type=float, default=1.0)
     ap.add_argument("--no-cublas-leg", action="store_true",
                     help="skip the same-process cuBLAS comparison and the one-second sustained legs (short runs under a profiler)")
+    ap.add_argument("--tile-n", type=int, default=0, choices=[0, 256, 512],
+                    help="bf16 workloads: columns of the CTA-pair tile (default 512: measured 4-5 %% ahead of 256 on the "
+                         "headline and 16 %% on the K-split, where the step runs under the power cap)")
     ap.add_argument("--tuning", default="", help="tuning string of the main workload's kernel spec, e.g. GROUP_M=4 or TAIL_SPLITS=1")
     ap.add_argument("--ksplit-exchange", default="fused", choices=["reduce", "fused", "nccl"],
                     help="K-split at 2+ GPUs: tiles added into the owner's buffer by the GEMM's own stores (reduce), stored "

@@ -23,7 +23,8 @@ constexpr int kSmemLimit = 232448;   // 227 KB of dynamic shared memory per CTA 
 int dense_smem_bytes(int cta_group, int block_n, int stages, int store_bufs, int row_bytes, int clc) {
     const int stage = (128 + block_n / cta_group) * row_bytes;
     const int sched = clc ? (2 * 4 + 1) * 8 + 48 : 0;     // the scheduler's ring: barriers, answer, tile ids
-    return stages * stage + 4 * store_bufs * 4096 + (2 * stages + 4) * 8 + 16 + sched + 1024;
+    const int epi_warps = block_n > 256 ? 8 : 4;
+    return stages * stage + epi_warps * store_bufs * 4096 + (2 * stages + 4) * 8 + 16 + sched + 1024;
 }
 int fp8_smem_bytes(int cta_group, int block_n, int stages, int promo_warps, int out_bytes) {
     const int stage = 128 * 128 + (block_n / cta_group) * 128;
@@ -193,6 +194,10 @@ int derive_config(const tesserae_kernel_spec& ks, KernelConfig* cfg, std::string
         if (msg) *msg = "IncompatibleTile: tile.n must be a multiple of " + std::to_string(std::max(chunk, 16 * c.cta_group)) +
                         " and <= 256 (512 for an unscaled CTA-pair kernel)";
         return spec::IncompatibleTile;
+    }
+    if (wide) {
+        c.threads += 128;              // eight epilogue warps: the one accumulator of the 512-column tile has to drain quickly
+        c.store_bufs = 1;              // one staging buffer per epilogue warp keeps four stages in shared memory
     }
     if (ks.scale_mode == TESSERAE_SCALE_FP8_BLOCK && ks.elem != TESSERAE_F8E4M3) {
         if (msg) *msg = "UnsupportedElem: FP8 block scaling needs elem F8E4M3";

@@ -382,6 +382,7 @@ static int pick_group_m(const KernelConfig& cfg, int64_t m, int64_t k) {
     const int64_t panel = tile_m * (k * tesserae::spec::elem_bits(cfg.elem) / 8);     // bytes of A per M-tile
     int64_t g = (int64_t(32) << 20) / (panel > 0 ? panel : 1);
     if (g < 8) g = 8;
+    if (cfg.block_n > 256) g *= 2;       // a wave of 512-column tiles spans half as many tile columns: keep its footprint near square
     if (g > 64) g = 64;
     if (g > num_m) g = num_m;
     return int(g < 1 ? 1 : g);
@@ -694,7 +695,7 @@ int tesserae_gemm_ksplit_scatter(tesserae_gemm_plan* p, const void* a, const voi
     const int op_swizzle = cfg.desc.swizzle.b;
     int rc = tesserae_tensor_map_2d(tm_a, cfg.elem, a, uint64_t(k), uint64_t(m), row_bytes, uint32_t(cfg.block_k), 128, op_swizzle);
     if (rc == 0) rc = tesserae_tensor_map_2d(tm_b, cfg.elem, b, uint64_t(k), uint64_t(n), row_bytes, uint32_t(cfg.block_k),
-                                             uint32_t(cfg.block_n / cfg.cta_group), op_swizzle);
+                                             uint32_t(cfg.b_box_rows), op_swizzle);
     for (int g = 0; g < n_dst && rc == 0; ++g) {
         const int64_t rows = (m - g * rows_per_owner) < rows_per_owner ? (m - g * rows_per_owner) : rows_per_owner;
         if (rows <= 0) break;

@@ -121,7 +121,10 @@ constexpr ts_u32 kOutBytes    = TS_OUT_F32 ? 4 : 2;
 constexpr ts_u32 kChunkCols   = 128 / kOutBytes;              // output columns per 128-byte staging row
 constexpr ts_u32 kNumChunks   = kBlockN / kChunkCols;
 constexpr ts_u32 kStoreBuf    = 32 * 128;                     // one warp's staging buffer: 32 rows x 128 B
-constexpr ts_u32 kNumEpiWarps = 4;
+// Four epilogue warps (one per 32-lane quarter of tensor memory); eight for the 512-column tile, two per quarter that
+// take alternate store chunks, because there the accumulator's hand-back is exposed and has to be quick.
+constexpr ts_u32 kNumEpiWarps = kHalves == 2 ? 8 : 4;
+constexpr ts_u32 kEpiSplit    = kNumEpiWarps / 4;             // warps that share a lane quarter
 #ifndef TS_STORE_BUFS
 #define TS_STORE_BUFS 2
 #endif
@@ -130,7 +133,7 @@ constexpr ts_u32 kSmemC       = kNumEpiWarps * kStoreBufs * kStoreBuf;
 constexpr ts_u32 kSchedRing   = 4;                            // tile ids in flight between the scheduler warp and the roles
 constexpr ts_u32 kNumBars     = 2 * kStages + kNumAcc + kNumAcc * kHalves + (TS_CLC ? 2 * kSchedRing + 1 : 0);
 constexpr ts_u32 kSmemTotal   = kStages * kStageBytes + kSmemC + kNumBars * 8 + 16 + (TS_CLC ? 48 : 0);
-constexpr ts_u32 kThreads     = 192 + (TS_CLC ? 32 : 0);      // producer, MMA issuer, four epilogue warps (+ scheduler)
+constexpr ts_u32 kThreads     = 64 + 32 * kNumEpiWarps + (TS_CLC ? 32 : 0);   // producer, MMA issuer, epilogue warps (+ scheduler)
 constexpr ts_u32 kNoTile      = 0xffffffffu;
 // Arrivals that hand a ring entry back: the producer lane of each CTA, the MMA warp (leader only), the epilogue warps.
 constexpr ts_u32 kSchedReaders = TS_CTA_GROUP + 1 + kNumEpiWarps * TS_CTA_GROUP;
@@ -138,6 +141,7 @@ constexpr ts_u32 kSchedReaders = TS_CTA_GROUP + 1 + kNumEpiWarps * TS_CTA_GROUP;
 static_assert(kBlockN % (16 * TS_CTA_GROUP) == 0 && kBlockN >= 16 * TS_CTA_GROUP && (kBlockN <= 256 || (kBlockN == 512 && TS_CTA_GROUP == 2)),
               "bad TS_BLOCK_N");
 static_assert(kNumChunks % kHalves == 0, "a store chunk must not straddle two MMA groups");
+static_assert((kNumChunks / kHalves) % kEpiSplit == 0, "the warps that share a lane quarter take equal shares of each MMA group");
 static_assert(kBlockN % kChunkCols == 0, "TS_BLOCK_N must be a multiple of the store chunk");
 static_assert(kNumAcc * kBlockN <= 512, "accumulators exceed tensor memory");
 static_assert(kSmemTotal + 1024 <= 232448, "shared memory over the 227 KB limit");
@@ -169,7 +173,7 @@ TS_DEV TileInfo tile_info(const TsGroupedProblem* probs, ts_u32 t, ts_u32& curso
 
 }  // namespace ts_dense
 
-extern "C" __global__ void __launch_bounds__(192 + (TS_CLC ? 32 : 0), 1)
+extern "C" __global__ void __launch_bounds__(64 + 32 * (TS_BLOCK_N > 256 ? 8 : 4) + (TS_CLC ? 32 : 0), 1)
 #if TS_GROUPED
 TS_KERNEL_NAME(const TsGroupedProblem* __restrict__ probs, int total_tiles, float alpha, ts_u32* __restrict__ status)
 #else
@@ -364,43 +368,72 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
 #endif
                 const ts_u32 acc = tile_iter % kNumAcc;
                 const ts_u32 acc_ph = (tile_iter / kNumAcc) & 1u;
-                // (the accumulator's column groups are waited for one by one, each in front of its first MMA)
                 const ts_u32 d_tmem = tmem_base + acc * kBlockN;
-                for (ts_u32 kb = 0; kb < ti.num_k_blocks; ++kb, ++it) {
-                    const ts_u32 s = it % kStages;
-                    const ts_u32 ph = (it / kStages) & 1u;
-                    if (!ts_mbar_wait(full_bar + 8 * s, ph)) {
-                        if (elected) atomicOr(status, TS_ERR_TIMEOUT_FULL);
-                        ok = false; break;
-                    }
-                    ts_tc_fence_after();
+                // The MMAs of column group h for the K block in stage s (one elected lane issues).
+                auto issue_group = [&](ts_u32 h, ts_u32 s, ts_u32 kb) {
                     const ts_u64 a_desc = ts_smem_desc_kmajor<TS_SWIZZLE_B>(smem_a + s * kSmemA);
+                    const ts_u64 b_desc = ts_smem_desc_kmajor<TS_SWIZZLE_B>(smem_b + s * kSmemB + h * kHalfRows * kBlockKBytes);
+                    if (elected) {
 #pragma unroll
-                    for (ts_u32 h = 0; h < kHalves; ++h) {
-                        if (kb == 0u) {
-                            // first MMA of this tile into column group h: the epilogue must have read the group out
-                            if (!ts_mbar_wait(tmem_empty_bar + 8 * (acc * kHalves + h), acc_ph ^ 1u)) {
-                                if (elected) atomicOr(status, TS_ERR_TIMEOUT_TMEM_EMPTY);
-                                ok = false; break;
-                            }
-                            ts_tc_fence_after();
-                        }
-                        const ts_u64 b_desc = ts_smem_desc_kmajor<TS_SWIZZLE_B>(smem_b + s * kSmemB + h * kHalfRows * kBlockKBytes);
-                        if (elected) {
-#pragma unroll
-                            for (ts_u32 k = 0; k < kNumUmma; ++k) {
-                                // +32 bytes along K inside the swizzle row = +2 in the address field
-                                ts_umma<TS_CTA_GROUP, TS_MMA_KIND>(d_tmem + h * kMmaN, a_desc + 2 * k, b_desc + 2 * k, idesc,
-                                                                   (kb | k) != 0u);
-                            }
+                        for (ts_u32 k = 0; k < kNumUmma; ++k) {
+                            // +32 bytes along K inside the swizzle row = +2 in the address field
+                            ts_umma<TS_CTA_GROUP, TS_MMA_KIND>(d_tmem + h * kMmaN, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0u);
                         }
                     }
-                    if (!ok) break;
+                };
+                // frees the smem stage (in both CTAs of a pair) once the MMAs issued so far have read it
+                auto free_stage = [&](ts_u32 s) {
                     if (elected) {
-                        // frees the smem stage (in both CTAs of a pair) once these MMAs have read it
                         if (TS_CTA_GROUP == 1) ts_umma_commit<1>(empty_bar + 8 * s);
                         else                   ts_umma_commit_pair(empty_bar + 8 * s, 3);
                     }
+                };
+                // The epilogue hands the accumulator back one column group at a time; each group is waited for in
+                // front of its first MMA.
+                auto wait_group = [&](ts_u32 h) -> bool {
+                    if (!ts_mbar_wait(tmem_empty_bar + 8 * (acc * kHalves + h), acc_ph ^ 1u)) {
+                        if (elected) atomicOr(status, TS_ERR_TIMEOUT_TMEM_EMPTY);
+                        return false;
+                    }
+                    ts_tc_fence_after();
+                    return true;
+                };
+                auto wait_stage = [&](ts_u32 i) -> bool {
+                    if (!ts_mbar_wait(full_bar + 8 * (i % kStages), (i / kStages) & 1u)) {
+                        if (elected) atomicOr(status, TS_ERR_TIMEOUT_FULL);
+                        return false;
+                    }
+                    ts_tc_fence_after();
+                    return true;
+                };
+                // With two column groups and one accumulator, the tile starts with group 0 alone for as many K blocks as
+                // the ring holds (their stages stay held), then group 1 for the same blocks: the epilogue of the tile
+                // before has that long to hand group 1 back after group 0.
+                ts_u32 head = 0;
+                if (kHalves == 2) {
+                    head = ti.num_k_blocks < kStages ? ti.num_k_blocks : kStages;
+                    ok = wait_group(0);
+                    for (ts_u32 kb = 0; kb < head && ok; ++kb) {
+                        ok = wait_stage(it + kb);
+                        if (ok) issue_group(0, (it + kb) % kStages, kb);
+                        __syncwarp();
+                    }
+                    if (ok) ok = wait_group(1);
+                    for (ts_u32 kb = 0; kb < head && ok; ++kb) {
+                        issue_group(1, (it + kb) % kStages, kb);
+                        free_stage((it + kb) % kStages);
+                        __syncwarp();
+                    }
+                    if (!ok) break;
+                    it += head;
+                }
+                for (ts_u32 kb = head; kb < ti.num_k_blocks; ++kb, ++it) {
+                    const ts_u32 s = it % kStages;
+                    if (!wait_stage(it)) { ok = false; break; }
+                    if (kb == 0u && !wait_group(0)) { ok = false; break; }       // (only reached with one column group)
+#pragma unroll
+                    for (ts_u32 h = 0; h < kHalves; ++h) issue_group(h, s, kb);
+                    free_stage(s);
                     __syncwarp();
                 }
                 if (!ok) break;
@@ -451,8 +484,11 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
             ts_tc_fence_after();
             const int row0 = (int)(m_blk * kTileM + cta_rank * kBlockM + quarter * 32);
             const ts_u32 t_row = tmem_base + ((quarter * 32u) << 16) + acc * kBlockN;
+            // (with two warps per lane quarter, warp `sub` takes chunks sub, sub + 2, ...: the first MMA group's chunks
+            // come first for every warp, so that group goes back to the MMA issuer after half the drain)
+            const ts_u32 sub = (warp_id - 2) / 4;
 #pragma unroll 1
-            for (ts_u32 j = 0; j < kNumChunks; ++j, ++chunk_iter) {
+            for (ts_u32 j = sub; j < kNumChunks; j += kEpiSplit, ++chunk_iter) {
                 const ts_u32 col0 = n_blk * kBlockN + j * kChunkCols;
                 const ts_u32 buf = store_smem + (chunk_iter % kStoreBufs) * kStoreBuf;
                 // the store that last read this staging buffer was issued kStoreBufs chunks ago
@@ -520,7 +556,7 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
 #endif
                     ts_bulk_commit();   // committed even when empty so that "one group pending" always means the previous chunk
                 }
-                if ((j + 1) % (kNumChunks / kHalves) == 0) {
+                if ((j + kEpiSplit) % (kNumChunks / kHalves) < kEpiSplit) {      // this warp's last chunk of an MMA group
                     // every column of one MMA group of this accumulator has been read: hand the group back to the MMA issuer
                     const ts_u32 grp = acc * kHalves + j / (kNumChunks / kHalves);
                     ts_tc_fence_before();
@@ -537,7 +573,7 @@ TS_KERNEL_NAME(const __grid_constant__ TsTensorMap tmap_a,
     }
 #if TS_CLC
     else {
-        // ------------------------------------------------------------ scheduler (warp 6, leader CTA, one lane)
+        // ------------------------------------------------------------ scheduler (the last warp, leader CTA, one lane)
         // Entry j of the ring: wait until every role of the pair has read what the entry held kSchedRing tiles ago,
         // ask the launch control for one more cluster's tile, and publish the answer (a tile id, or kNoTile once
         // nothing is left to cancel) to both CTAs: the id with a store to the CTA's shared memory, then an arrive

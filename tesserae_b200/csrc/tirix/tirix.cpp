@@ -275,7 +275,7 @@ Program lower(const KernelConfig& c, const tesserae_kernel_spec& ks) {
         if (!fp8blk) { tile.push_back(barrier(OpKind::Tcgen05FenceBefore)); tile.push_back(barrier(OpKind::WarpSync)); tile.push_back(release); }
         tile.push_back(assign("tile_iter", "tile_iter + 1"));
         take_next(tile);
-        const std::string who = fp8blk ? "warp_id >= 4" : nvfp4 ? "warp_id >= 2 && warp_id < 10" : c.clc ? "warp_id >= 2 && warp_id < 6" : "warp_id >= 2";
+        const std::string who = fp8blk ? "warp_id >= 4" : nvfp4 ? "warp_id >= 2 && warp_id < 10" : c.clc ? "warp_id >= 2 && warp_id < " + std::to_string(warps - 1) : "warp_id >= 2";
         b.push_back(group(spec::Epilogue, {iff(who, {let("tile_iter", "0", true), let("taken", "0", true),
                                                      forr("t", "first_tile", "num_tiles", "tile_step", tile)})}));
     }

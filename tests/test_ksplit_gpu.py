@@ -106,9 +106,10 @@ def test_config5_shard_properties(torch_cuda, plan_f32):
     assert float((halves[0] + halves[1] - whole).abs().max()) <= 1e-3 * float(whole.abs().max())
 
 
-def test_scatter_epilogue_matches_plain_partial(torch_cuda, plan_f32):
+@pytest.mark.parametrize("tile_n", [256, 512])
+def test_scatter_epilogue_matches_plain_partial(torch_cuda, plan_f32, tile_n):
     """The row-scattered epilogue (the GEMM -> reduce-scatter fusion) with all destinations on this GPU: owner g's
-    buffer must hold exactly rows [g*R, (g+1)*R) of the ordinary fp32 partial, bit for bit."""
+    buffer must hold exactly rows [g*R, (g+1)*R) of the ordinary fp32 partial, bit for bit (both tile widths)."""
     t = torch_cuda
     m, n, k, owners = 1024 + 256, 768, 1024, 4          # the last owner gets a short slice
     rpo = 384
@@ -118,8 +119,8 @@ def test_scatter_epilogue_matches_plain_partial(torch_cuda, plan_f32):
     s = t.cuda.current_stream().cuda_stream
     plain = t.empty((m, n), dtype=t.float32, device="cuda")
     plan_f32.ksplit_partials(a, b, plain, plain.numel() * 4, m, n, k, 1, stream=s)
-    scat = api.GemmPlan(api.KernelSpec(name="gemm_bf16_cg2_f32_scatter", elem=api.BF16, tile=(128, 256, 64), cta_group=2,
-                                       out_elem=api.F32, scatter=1))
+    scat = api.GemmPlan(api.KernelSpec(name="gemm_bf16_cg2_f32_scatter" + ("" if tile_n == 256 else f"_n{tile_n}"), elem=api.BF16,
+                                       tile=(128, tile_n, 64), cta_group=2, out_elem=api.F32, scatter=1))
     dst = [t.full((rpo, n), float("nan"), dtype=t.float32, device="cuda") for _ in range(owners)]
     scat.ksplit_scatter(a, b, [d.data_ptr() for d in dst], rpo, m, n, k, stream=s, start_owner=2)   # a rotated tile order
     assert scat.status() == 0 and plan_f32.status() == 0
@@ -169,7 +170,8 @@ def test_config5_full_size(torch_cuda, plan_f32):
     assert np.max(np.abs(got_rowsum - want_rowsum)) <= 1e-3 * float(np.sqrt(np.mean(want_rowsum ** 2)))
 
 
-def test_scatter_add_epilogue_matches_plain_partial(torch_cuda, plan_f32):
+@pytest.mark.parametrize("tile_n", [256, 512])
+def test_scatter_add_epilogue_matches_plain_partial(torch_cuda, plan_f32, tile_n):
     """The adding form of the row-scattered epilogue (TMA reduce at the destination) with all owners on this GPU:
     into zeroed buffers it must leave exactly the rows of the ordinary fp32 partial (0 + x = x), and a second launch
     on top of the first exactly twice that (x + x is exact in fp32)."""
@@ -182,8 +184,8 @@ def test_scatter_add_epilogue_matches_plain_partial(torch_cuda, plan_f32):
     s = t.cuda.current_stream().cuda_stream
     plain = t.empty((m, n), dtype=t.float32, device="cuda")
     plan_f32.ksplit_partials(a, b, plain, plain.numel() * 4, m, n, k, 1, stream=s)
-    radd = api.GemmPlan(api.KernelSpec(name="gemm_bf16_cg2_f32_scatter_add", elem=api.BF16, tile=(128, 256, 64),
-                                       cta_group=2, out_elem=api.F32, scatter=2))
+    radd = api.GemmPlan(api.KernelSpec(name="gemm_bf16_cg2_f32_scatter_add" + ("" if tile_n == 256 else f"_n{tile_n}"), elem=api.BF16,
+                                       tile=(128, tile_n, 64), cta_group=2, out_elem=api.F32, scatter=2))
     dst = [t.zeros((rpo, n), dtype=t.float32, device="cuda") for _ in range(owners)]
     for times in (1, 2):
         radd.ksplit_scatter(a, b, [d.data_ptr() for d in dst], rpo, m, n, k, stream=s)
