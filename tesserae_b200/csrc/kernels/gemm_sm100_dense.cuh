@@ -9,9 +9,10 @@
 // (bm + bn/2) * bk * bytes for a CTA pair (lib/pipeline/tile_io.ml:119-127).
 //
 // Differences from that sketch, all needed for a kernel that runs: 4 epilogue warps
-// (warps 2..5, one per 32-lane TMEM quarter), empty-slot barriers armed by tcgen05.commit,
-// a persistent tile loop with two TMEM accumulator buffers (lib/pipeline/tmem.ml:106-110)
-// so that the epilogue of tile i overlaps the mainloop of tile i+1, a real instruction
+// (warps 2..5, one per 32-lane TMEM quarter; 8 for the 512-column tile), empty-slot barriers
+// armed by tcgen05.commit, a persistent tile loop with two TMEM accumulator buffers
+// (lib/pipeline/tmem.ml:106-110) so that the epilogue of tile i overlaps the mainloop of tile
+// i+1 (one buffer, handed back in two column groups, for the 512-column tile), a real instruction
 // descriptor and shared-memory descriptors, a TMA-store epilogue with fused alpha, bias
 // and cast, and bounded waits.  The SM100 load strategy tag of the reference
 // (lib/pipeline/tile_io.ml:28-32) is lowered to per-CTA TMA loads: in a CTA pair each CTA
@@ -21,7 +22,8 @@
 // Compile-time configuration (macros, set by the emitter in front of this text):
 //   TS_KERNEL_NAME   extern "C" symbol
 //   TS_CTA_GROUP     1 or 2 (CTAs per MMA; 2 needs cluster dims (2,1,1))
-//   TS_BLOCK_N       tile width = MMA N (multiple of 16*TS_CTA_GROUP, <= 256)
+//   TS_BLOCK_N       tile width (multiple of 16*TS_CTA_GROUP, <= 256: one MMA per K step; or 512 for a CTA pair: two
+//                    MMA groups of 256 columns per K step, 320 threads -- see kMmaN below)
 //   TS_STAGES        depth of the smem ring
 //   TS_ELEM_BYTES    2 (bf16/f16) or 1 (e4m3)
 //   TS_SWIZZLE_B     B of the operand tiles' Swizzle<B,4,3> (1..3), as Swizzle.smem_selector derives it from the
@@ -54,7 +56,7 @@
 //   TS_CLC           0/1: dynamic tile order by cluster launch control -- the role the reference reserves a warp for
 //                    (lib/pipeline/cluster.mli:17-21: "Scheduler: issues CLC try_cancel, feeds tile ids").  The grid
 //                    has one cluster per tile instead of one per SM (pair).  Every cluster that runs computes its own
-//                    tile and then, through its scheduler warp (warp 6 of the leader CTA), asks the hardware to
+//                    tile and then, through its scheduler warp (the last warp of the leader CTA), asks the hardware to
 //                    cancel a cluster that has not started yet and takes that cluster's tile, until no cluster is
 //                    left to cancel.  A cluster that finishes a short tile early takes the next tile at once, so
 //                    tiles of unequal length (a grouped launch of problems with different K) do not wait for a
