@@ -328,3 +328,18 @@ def test_wide_tile_equals_narrow(torch_cuda, out_elem, bias, tuning):
         want = run_gpu(torch, narrow, p, m, n, k, out_elem, alpha=0.75)
         assert not np.isnan(got).any(), (m, n, k)
         assert np.array_equal(got, want), (m, n, k)
+    if out_elem == api.BF16 and not tuning:
+        # config 2 at full size (8192^3, N(0,1) * 0.05 drawn on the GPU): the wide tile against the narrow one, bit for bit
+        from helpers import fullsize as F
+        m = n = k = 8192
+        a = F.draw(torch, (m, k), 1, "normal", 0.05).to(torch.bfloat16)
+        b = F.draw(torch, (n, k), 1001, "normal", 0.05).to(torch.bfloat16)
+        bias_d = (F.draw(torch, (n,), 2001, "normal", 0.1)).to(torch.bfloat16)
+        st = torch.cuda.current_stream().cuda_stream
+        c_wide = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+        c_narrow = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+        wide.run(a, b, c_wide, bias_d, 1.0, m, n, k, stream=st)
+        narrow.run(a, b, c_narrow, bias_d, 1.0, m, n, k, stream=st)
+        torch.cuda.synchronize()
+        assert wide.status() == 0 and narrow.status() == 0
+        assert torch.equal(c_wide.view(torch.int16), c_narrow.view(torch.int16))
