@@ -231,7 +231,9 @@ typedef struct tesserae_kernel_spec {
     const char* name;
     int arch;        /* TESSERAE_SM* */
     int elem;        /* TESSERAE_* element code of A and B */
-    int tile_m, tile_n, tile_k;
+    int tile_m, tile_n, tile_k;   /* 128 rows per CTA; tile_n a multiple of 16 per CTA (and of the 128-byte store chunk) up
+                                     to 256, or 512 for an unscaled CTA-pair kernel; tile_k elements spanning 32, 64 or
+                                     128 bytes (128 for the block-scaled kernels) */
     int stages;      /* ignored by Lower.lower, like the reference; 0 = choose by smem */
     int cta_group;   /* 0 or 2: CTA pair (reference), 1: single CTA */
     int out_elem;    /* 0 or TESSERAE_F32: fp32 C (reference); TESSERAE_BF16: bf16 C */
