@@ -2,6 +2,7 @@
 """Benchmark of the dense GEMM hot path on N B200s of one node.
 
     python bench.py --gpus N --steps K --warmup W [--workload NAME] [--sub-configs all|none] [--impl reference]
+                    [--tile-n 256|512] [--tuning "NAME=VALUE;..."] [--ksplit-exchange fused|reduce|nccl]
 
 One step = one pass of the hot path over the workload: one GEMM launch per GPU (plus, for the
 K-split workload, the reduce-scatter of the fp32 partials and the sum + bf16 cast).  Rank 0
@@ -22,8 +23,9 @@ Workloads (BASELINE.json configs):
                                partials + bf16 cast: strong scaling; compute and communication
                                reported separately.
 The default run measures the headline workload and then, in the same process and at the same N,
-fp8_block, nvfp4 and bf16_ksplit (with both exchanges at N > 1); their records go into the line's
-`configs` object.  Operand sources are drawn on the GPU from a seeded Philox generator (the host
+fp8_block, nvfp4 and bf16_ksplit (with all three exchanges at N > 1); their records go into the line's
+`configs` object.  The bf16 workloads run the CTA-pair kernel with the 512-column tile (--tile-n 256
+selects the narrower one).  Operand sources are drawn on the GPU from a seeded Philox generator (the host
 generator needs minutes for 10^9 values) and quantised by the library's own GPU quantisers.
 """
 from __future__ import annotations
